@@ -1,0 +1,162 @@
+/*
+ * pdw_b200.h - C ABI of the B200 (sm_100a) hot path of PyramidConvBlock.
+ *
+ * One shared library (libpdw_b200.so) replaces the six Triton kernels of the reference
+ * package `pyramid_dwconv` and adds the backward passes the reference leaves to ATen.
+ * Every entry point takes raw device pointers, plain integers and a CUDA stream; no
+ * torch type crosses this boundary.  The library never allocates, frees or synchronises:
+ * the caller owns inputs, outputs and scratch ("workspace") memory.  All tensors are
+ * dense NHWC ([B,H,W,C], C fastest), weights are [KH,KW,C], exactly the layouts of the
+ * reference (pyramid_dwconv/dwconv_triton.py:49,67-72,78-83).
+ *
+ * Return value of every function that launches work: 0 on success, otherwise one of
+ * the PDW_ERR_* codes below (pdw_status_string() gives text).  Nothing falls back to a
+ * CPU implementation.
+ *
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ * `dtype` is one of PDW_F32 / PDW_F16 / PDW_BF16 and applies to every tensor of the
+ * call; accumulation is always fp32.
+ */
+#ifndef PDW_B200_H
+#define PDW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { PDW_F32 = 0, PDW_F16 = 1, PDW_BF16 = 2 };
+
+enum {
+    PDW_OK = 0,
+    PDW_ERR_NULL_POINTER = 1,
+    PDW_ERR_BAD_DTYPE = 2,
+    PDW_ERR_BAD_SHAPE = 3,      /* non-positive extent, output size mismatch, int32 overflow */
+    PDW_ERR_UNSUPPORTED = 4,    /* e.g. backward with parameters the gather form cannot invert */
+    PDW_ERR_WORKSPACE = 5,      /* workspace pointer missing or too small */
+    PDW_ERR_MISALIGNED = 6,     /* a pointer is not aligned to its element size */
+    PDW_ERR_CUDA = 7,           /* a CUDA runtime/driver call failed; see pdw_last_cuda_error() */
+    PDW_ERR_DEVICE_TIMEOUT = 8, /* a bounded device-side wait ran out (reported via status word) */
+    PDW_ERR_TOO_LARGE = 9       /* request exceeds a fixed capacity of the entry point */
+};
+
+/* Geometry of one depthwise convolution; mirrors the argument list of the reference kernels
+ * (pyramid_dwconv/dwconv_triton.py:20-26). */
+typedef struct pdw_conv_geom {
+    int32_t batch, in_h, in_w, channels;
+    int32_t kernel_h, kernel_w;
+    int32_t stride_h, stride_w;
+    int32_t pad_h, pad_w;
+    int32_t dil_h, dil_w;
+} pdw_conv_geom;
+
+/* Library identification. */
+int pdw_version(void);
+const char* pdw_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call on the calling thread (0 if none). */
+int pdw_last_cuda_error(void);
+
+/* Output extent of a convolution along one axis, the formula of
+ * pyramid_dwconv/dwconv_triton.py:311-312. */
+int pdw_conv_out_size(int in, int kernel, int stride, int pad, int dil);
+
+/*
+ * Depthwise cross-correlation, zero padding, optional bias fused into the accumulator:
+ *   y[b,oh,ow,c] = bias[c] + sum_{kh,kw} x[b, oh*s-p+kh*d, ow*s-p+kw*d, c] * w[kh,kw,c]
+ * Replaces _depthwise_conv_kernel_optimized (pyramid_dwconv/dwconv_triton.py:20-104) and its
+ * launch in DepthwiseConv2DFunction.forward (:301-336).  `bias` may be NULL (the reference has
+ * no bias).  `status_word` may be NULL; if given it must point to a zero-initialised int32 in
+ * device memory that the kernels set to PDW_ERR_DEVICE_TIMEOUT when a bounded wait on a
+ * shared-memory barrier runs out.
+ */
+int pdw_dwconv_fwd(const void* x, const void* w, const void* bias, void* y,
+                   const pdw_conv_geom* g, int dtype, int32_t* status_word, void* stream);
+
+/*
+ * Gradient w.r.t. the input: dx = correlation of grad_out with the kernel flipped on both axes.
+ * Replaces _depthwise_conv_backward_input_kernel (pyramid_dwconv/dwconv_triton.py:119-203) and the
+ * redundant zero fill before it (:346).  Unlike the reference, which is only right for stride 1 with
+ * 2*pad == (k-1)*dil, every stride / padding / dilation is handled.  `g` describes the FORWARD
+ * convolution; grad_out is [B,OH,OW,C], dx is [B,in_h,in_w,C].
+ */
+int pdw_dwconv_bwd_input(const void* grad_out, const void* w, void* dx,
+                         const pdw_conv_geom* g, int dtype, int32_t* status_word, void* stream);
+
+/*
+ * Gradient w.r.t. weight and (optionally) bias in one pass over grad_out:
+ *   dw[kh,kw,c] = sum_{b,oh,ow} grad_out[b,oh,ow,c] * x[b, oh*s-p+kh*d, ow*s-p+kw*d, c]
+ *   dbias[c]    = sum_{b,oh,ow} grad_out[b,oh,ow,c]
+ * Replaces _depthwise_conv_weight_grad_kernel (pyramid_dwconv/dwconv_triton.py:219-296): instead of
+ * k*k*C floating-point atomics per program into a 16-bit buffer, partial sums stay in registers,
+ * are combined with warp shuffles, written once per thread block as fp32 into `workspace`, and a
+ * second kernel adds the per-block partials in a fixed order (bitwise reproducible).  `dbias` may be
+ * NULL.  dw/dbias are written in `dtype` unless `out_fp32` is non-zero, in which case they are
+ * float32 (useful as the source of an all-reduce).  `workspace` needs pdw_dwconv_bwd_weight_workspace()
+ * bytes, 16-byte aligned.
+ */
+size_t pdw_dwconv_bwd_weight_workspace(const pdw_conv_geom* g, int dtype);
+int pdw_dwconv_bwd_weight(const void* x, const void* grad_out, void* dw, void* dbias,
+                          const pdw_conv_geom* g, int dtype, int out_fp32,
+                          void* workspace, size_t workspace_bytes,
+                          int32_t* status_word, void* stream);
+
+/*
+ * Adaptive average pooling, window [floor(i*in/out), ceil((i+1)*in/out)) per axis in exact integer
+ * arithmetic.  Replaces _adaptive_avg_pool_kernel (pyramid_dwconv/avgpool_triton.py:14-107) and the
+ * F.adaptive_avg_pool2d call of SimpleGate (pyramid_dwconv/conv_block.py:16).  x [B,H,W,C] -> y [B,OH,OW,C].
+ */
+int pdw_pool_fwd(const void* x, void* y, int batch, int in_h, int in_w, int channels,
+                 int out_h, int out_w, int dtype, void* stream);
+
+/*
+ * Backward of the above in gather form (every dx element is written exactly once, no atomics, no
+ * zero fill).  Replaces _adaptive_avg_pool_grad_kernel (pyramid_dwconv/avgpool_triton.py:118-203).
+ * grad_out [B,OH,OW,C] -> dx [B,H,W,C].
+ */
+int pdw_pool_bwd(const void* grad_out, void* dx, int batch, int in_h, int in_w, int channels,
+                 int out_h, int out_w, int dtype, void* stream);
+
+/*
+ * Bilinear resize with align_corners=False source coordinates
+ *   src = max((dst + 0.5) * in/out - 0.5, 0), weights in fp32.
+ * Replaces _bilinear_interp_kernel (pyramid_dwconv/up_triton.py:14-125) and the F.interpolate call of
+ * SimpleGate (pyramid_dwconv/conv_block.py:21).  x [B,h,w,C] -> y [B,H,W,C].
+ */
+int pdw_upsample_fwd(const void* x, void* y, int batch, int in_h, int in_w, int channels,
+                     int out_h, int out_w, int dtype, void* stream);
+
+/*
+ * Adjoint of pdw_upsample_fwd in gather form: dx[iy,ix] = sum over the output pixels whose 2x2
+ * footprint touches (iy,ix) of weight * grad_out.  The reference's up_triton.py has no backward;
+ * inside ConvBlock the gradient of conv_block.py:21 is ATen's upsample_bilinear2d_backward, whose
+ * result this reproduces.  grad_out [B,H,W,C] -> dx [B,h,w,C] (in_h,in_w are the forward INPUT size).
+ */
+int pdw_upsample_bwd(const void* grad_out, void* dx, int batch, int in_h, int in_w, int channels,
+                     int out_h, int out_w, int dtype, void* stream);
+
+/*
+ * The gate of SimpleGate (pyramid_dwconv/conv_block.py:18-19): the conv output [N, C] (N = B*H*W
+ * pixels) is split into halves x1 = [:, :C/2], x2 = [:, C/2:], and y = x1 * (x2 * inv_scale) with
+ * inv_scale = 1 / (dim/2)^-0.5.  One kernel instead of chunk + div + mul.
+ */
+int pdw_gate_fwd(const void* conv_out, void* y, int64_t pixels, int channels, float inv_scale,
+                 int dtype, void* stream);
+/* d(conv_out) from d(y): [:, :C/2] = gy * x2 * inv_scale, [:, C/2:] = gy * x1 * inv_scale. */
+int pdw_gate_bwd(const void* conv_out, const void* grad_y, void* grad_conv_out, int64_t pixels,
+                 int channels, float inv_scale, int dtype, void* stream);
+
+/*
+ * Experiment hook, not part of the reference surface: selects between equivalent inner-loop
+ * code paths of the tiled convolution kernels (key 0: arithmetic form for 16-bit inputs,
+ * 0 = packed-pair FP32 FMA after conversion, 1 = mixed-precision FMA on the 16-bit operands;
+ * key 1: channels per thread block tile, 16 or 32; key 2: force the untiled kernels when 1).
+ * Results are identical for every setting.  Returns the previous value, or -1 for a bad key.
+ */
+int pdw_set_tuning(int key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PDW_B200_H */

@@ -1,0 +1,188 @@
+"""CPU oracle of the PyramidConvBlock hot path.  TEST INFRASTRUCTURE ONLY.
+
+Two layers:
+
+* ``c_*`` functions: ctypes calls into ``pdw_oracle.c`` (plain C loops, double accumulation), one
+  per kernel of the reference.  Parity pin: checked in tests/test_oracle.py against the golden
+  fixtures produced by the unmodified reference (tests/golden/make_golden.py) and against the torch
+  CPU ops.
+* ``torch_*`` functions: the composition the reference names as its own CPU equivalent and uses as
+  comparator in its benchmark scripts - ``F.conv2d(groups=C)`` with the weight mapped as in
+  pyramid_dwconv/dwconv_triton.py:457, ``F.adaptive_avg_pool2d`` and bilinear ``F.interpolate``
+  exactly as SimpleGate calls them (pyramid_dwconv/conv_block.py:16,21).  ``ref_block_forward``
+  restates ``ConvBlock.forward`` (conv_block.py:36-49) over these ops for any dtype, including
+  float64.  This layer is also what bench.py times as the CPU baseline.
+
+Nothing in the product package imports this module.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(HERE, "_build", "libpdw_oracle.so")
+_lib = None
+
+
+def build():
+    """Compile pdw_oracle.c with gcc if the library is missing or older than the source."""
+    src = os.path.join(HERE, "pdw_oracle.c")
+    if not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        os.makedirs(os.path.dirname(_LIB_PATH), exist_ok=True)
+        subprocess.run(["gcc", "-O2", "-fPIC", "-shared", "-o", _LIB_PATH, src, "-lm"], check=True)
+    return _LIB_PATH
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+    return _lib
+
+
+def _f32(a):
+    if isinstance(a, torch.Tensor):
+        a = a.detach().cpu().float().numpy()
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+
+def _pair(v):
+    return (int(v[0]), int(v[1])) if isinstance(v, (tuple, list)) else (int(v), int(v))
+
+
+def conv_out_hw(H, W, k, stride, padding, dilation):
+    return ((H + 2 * padding[0] - dilation[0] * (k[0] - 1) - 1) // stride[0] + 1,
+            (W + 2 * padding[1] - dilation[1] * (k[1] - 1) - 1) // stride[1] + 1)
+
+
+# ---------------------------------------------------------------------------------------------
+# C oracle
+# ---------------------------------------------------------------------------------------------
+def c_dwconv_fwd(x, w, bias=None, stride=1, padding=0, dilation=1):
+    x, w = _f32(x), _f32(w)
+    bias = None if bias is None else _f32(bias)
+    s, p, d = _pair(stride), _pair(padding), _pair(dilation)
+    B, H, W, C = x.shape
+    KH, KW = w.shape[:2]
+    OH, OW = conv_out_hw(H, W, (KH, KW), s, p, d)
+    y = np.empty((B, OH, OW, C), np.float32)
+    _load().oracle_dwconv_fwd(_p(x), _p(w), _p(bias), _p(y), B, H, W, C, KH, KW, s[0], s[1], p[0], p[1], d[0], d[1])
+    return y
+
+
+def c_dwconv_bwd_input(gout, w, input_hw, stride=1, padding=0, dilation=1):
+    gout, w = _f32(gout), _f32(w)
+    s, p, d = _pair(stride), _pair(padding), _pair(dilation)
+    B, C = gout.shape[0], gout.shape[3]
+    H, W = int(input_hw[0]), int(input_hw[1])
+    KH, KW = w.shape[:2]
+    dx = np.empty((B, H, W, C), np.float32)
+    _load().oracle_dwconv_bwd_input(_p(gout), _p(w), _p(dx), B, H, W, C, KH, KW, s[0], s[1], p[0], p[1], d[0], d[1])
+    return dx
+
+
+def c_dwconv_bwd_weight(x, gout, kernel_size, stride=1, padding=0, dilation=1):
+    x, gout = _f32(x), _f32(gout)
+    s, p, d = _pair(stride), _pair(padding), _pair(dilation)
+    KH, KW = _pair(kernel_size)
+    B, H, W, C = x.shape
+    dw = np.empty((KH, KW, C), np.float32)
+    db = np.empty((C,), np.float32)
+    _load().oracle_dwconv_bwd_weight(_p(x), _p(gout), _p(dw), _p(db), B, H, W, C, KH, KW, s[0], s[1], p[0], p[1],
+                                     d[0], d[1])
+    return dw, db
+
+
+def _resample(name, src, out_shape, H, W, OH, OW):
+    src = _f32(src)
+    dst = np.empty(out_shape, np.float32)
+    getattr(_load(), name)(_p(src), _p(dst), src.shape[0], H, W, src.shape[3], OH, OW)
+    return dst
+
+
+def c_pool_fwd(x, output_size):
+    OH, OW = _pair(output_size)
+    B, H, W, C = x.shape
+    return _resample("oracle_pool_fwd", x, (B, OH, OW, C), H, W, OH, OW)
+
+
+def c_pool_bwd(gout, input_hw):
+    B, OH, OW, C = gout.shape
+    H, W = int(input_hw[0]), int(input_hw[1])
+    return _resample("oracle_pool_bwd", gout, (B, H, W, C), H, W, OH, OW)
+
+
+def c_upsample_fwd(x, output_size):
+    OH, OW = _pair(output_size)
+    B, H, W, C = x.shape
+    return _resample("oracle_upsample_fwd", x, (B, OH, OW, C), H, W, OH, OW)
+
+
+def c_upsample_bwd(gout, input_hw):
+    B, OH, OW, C = gout.shape
+    H, W = int(input_hw[0]), int(input_hw[1])
+    return _resample("oracle_upsample_bwd", gout, (B, H, W, C), H, W, OH, OW)
+
+
+# ---------------------------------------------------------------------------------------------
+# torch CPU composition (the reference's named CPU equivalent)
+# ---------------------------------------------------------------------------------------------
+def torch_dwconv(x, w, bias=None, stride=1, padding=0, dilation=1):
+    """NHWC depthwise conv through F.conv2d(groups=C); weight [KH,KW,C] -> [C,1,KH,KW]
+    (the mapping of pyramid_dwconv/dwconv_triton.py:457)."""
+    C = x.shape[-1]
+    y = F.conv2d(x.permute(0, 3, 1, 2), w.permute(2, 0, 1).unsqueeze(1), bias, stride=stride, padding=padding,
+                 dilation=dilation, groups=C)
+    return y.permute(0, 2, 3, 1)
+
+
+def torch_pool(x, output_size):
+    return F.adaptive_avg_pool2d(x.permute(0, 3, 1, 2), output_size).permute(0, 2, 3, 1)
+
+
+def torch_upsample(x, output_size):
+    return F.interpolate(x.permute(0, 3, 1, 2), size=output_size, mode="bilinear",
+                         align_corners=False).permute(0, 2, 3, 1)
+
+
+def torch_gate_branch(x, w, scale_factor, bias=None):
+    """SimpleGate.forward, pyramid_dwconv/conv_block.py:13-22."""
+    B, H, W, C = x.shape
+    k = w.shape[0]
+    scale = (C / 2) ** -0.5
+    if scale_factor != 1.:
+        x = torch_pool(x, (int(H * scale_factor), int(W * scale_factor)))
+    x = torch_dwconv(x, w, bias, padding=k // 2)
+    x1, x2 = x.chunk(2, dim=-1)
+    x = x1 * (x2 / scale)
+    if scale_factor != 1.:
+        x = torch_upsample(x, (H, W))
+    return x
+
+
+def ref_block_forward(x, params, scales=(1., 1 / 2)):
+    """ConvBlock.forward, pyramid_dwconv/conv_block.py:36-49, from a state_dict-like mapping."""
+    t = F.linear(x, params["conv_up.weight"], params.get("conv_up.bias"))
+    outs = [torch_gate_branch(t, params["gates.%d.conv_spatial.weight" % i], s) for i, s in enumerate(scales)]
+    t = torch.cat(outs, dim=-1)
+    t = F.linear(t, params["conv_out.weight"], params.get("conv_out.bias"))
+    pooled = x.mean(dim=(1, 2), keepdim=True)
+    pooled = F.linear(pooled, params["conv_pool.weight"], params.get("conv_pool.bias"))
+    return t + pooled
+
+
+def ref_block_forward_backward(x, gout, params, dtype=torch.float64, scales=(1., 1 / 2)):
+    """Forward + backward of the block in ``dtype`` on the CPU: (y, dx, {name: grad})."""
+    x = x.detach().to(dtype).requires_grad_(True)
+    ps = {k: v.detach().to(dtype).requires_grad_(True) for k, v in params.items()}
+    y = ref_block_forward(x, ps, scales)
+    y.backward(gout.to(dtype))
+    return y.detach(), x.grad, {k: v.grad for k, v in ps.items()}

@@ -1,0 +1,96 @@
+"""ctypes binding of libpdw_b200.so, the C-ABI library declared in include/pdw_b200.h.
+
+There is deliberately no alternative implementation behind these functions: if the shared
+library is missing or a call fails, a RuntimeError is raised.
+"""
+import ctypes
+import os
+import threading
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libpdw_b200.so")
+
+PDW_F32, PDW_F16, PDW_BF16 = 0, 1, 2
+PDW_ERR_DEVICE_TIMEOUT = 8
+
+# Every symbol that include/pdw_b200.h declares; tests check that the built library exports all.
+EXPORTED_SYMBOLS = (
+    "pdw_version", "pdw_status_string", "pdw_last_cuda_error", "pdw_conv_out_size",
+    "pdw_dwconv_fwd", "pdw_dwconv_bwd_input", "pdw_dwconv_bwd_weight_workspace", "pdw_dwconv_bwd_weight",
+    "pdw_pool_fwd", "pdw_pool_bwd", "pdw_upsample_fwd", "pdw_upsample_bwd",
+    "pdw_gate_fwd", "pdw_gate_bwd", "pdw_set_tuning",
+)
+
+
+class ConvGeom(ctypes.Structure):
+    """Mirror of ``pdw_conv_geom``."""
+    _fields_ = [(name, ctypes.c_int32) for name in (
+        "batch", "in_h", "in_w", "channels", "kernel_h", "kernel_w",
+        "stride_h", "stride_w", "pad_h", "pad_w", "dil_h", "dil_w")]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def _declare(lib):
+    vp, i32, i64, f32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
+    geom = ctypes.POINTER(ConvGeom)
+    lib.pdw_version.restype = i32
+    lib.pdw_version.argtypes = []
+    lib.pdw_status_string.restype = ctypes.c_char_p
+    lib.pdw_status_string.argtypes = [i32]
+    lib.pdw_last_cuda_error.restype = i32
+    lib.pdw_last_cuda_error.argtypes = []
+    lib.pdw_conv_out_size.restype = i32
+    lib.pdw_conv_out_size.argtypes = [i32] * 5
+    lib.pdw_dwconv_fwd.restype = i32
+    lib.pdw_dwconv_fwd.argtypes = [vp, vp, vp, vp, geom, i32, vp, vp]
+    lib.pdw_dwconv_bwd_input.restype = i32
+    lib.pdw_dwconv_bwd_input.argtypes = [vp, vp, vp, geom, i32, vp, vp]
+    lib.pdw_dwconv_bwd_weight_workspace.restype = sz
+    lib.pdw_dwconv_bwd_weight_workspace.argtypes = [geom, i32]
+    lib.pdw_dwconv_bwd_weight.restype = i32
+    lib.pdw_dwconv_bwd_weight.argtypes = [vp, vp, vp, vp, geom, i32, i32, vp, sz, vp, vp]
+    for name in ("pdw_pool_fwd", "pdw_pool_bwd", "pdw_upsample_fwd", "pdw_upsample_bwd"):
+        fn = getattr(lib, name)
+        fn.restype = i32
+        fn.argtypes = [vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.pdw_gate_fwd.restype = i32
+    lib.pdw_gate_fwd.argtypes = [vp, vp, i64, i32, f32, i32, vp]
+    lib.pdw_gate_bwd.restype = i32
+    lib.pdw_gate_bwd.argtypes = [vp, vp, vp, i64, i32, f32, i32, vp]
+    lib.pdw_set_tuning.restype = i32
+    lib.pdw_set_tuning.argtypes = [i32, i32]
+    if hasattr(lib, "pdw_dwconv_bwd_weight_static"):
+        lib.pdw_dwconv_bwd_weight_static.restype = i32
+        lib.pdw_dwconv_bwd_weight_static.argtypes = [vp, vp, vp, vp, geom, i32, i32, vp, vp]
+        lib.pdw_static_scratch_bytes.restype = sz
+        lib.pdw_static_scratch_bytes.argtypes = []
+
+
+def lib():
+    """The loaded library (loaded on first use)."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        "libpdw_b200.so is not built (%s). Run `python -m pyramidconvblock_b200.build`; "
+                        "there is no fallback implementation." % LIB_PATH)
+                handle = ctypes.CDLL(LIB_PATH)
+                _declare(handle)
+                _lib = handle
+    return _lib
+
+
+def check(status, what):
+    """Raise RuntimeError for a non-zero status code of the library."""
+    if status != 0:
+        L = lib()
+        msg = L.pdw_status_string(status).decode()
+        extra = ""
+        if status == 7:
+            extra = " (cuda error %d)" % L.pdw_last_cuda_error()
+        raise RuntimeError("%s failed: %s%s" % (what, msg, extra))

@@ -1,0 +1,100 @@
+"""Builds libpdw_b200.so (the C-ABI library of sm_100a kernels) in-tree with nvcc.
+
+    python -m pyramidconvblock_b200.build [--force] [--verbose]
+
+Objects go to ``csrc/build/``; the library lands beside this file so that it travels with the
+package.  The per-filter-width translation unit ``dwconv_k.cu`` is compiled once per supported
+width, all objects in parallel.
+"""
+import concurrent.futures
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ_DIR = os.path.join(CSRC, "build")
+LIB_PATH = os.path.join(HERE, "libpdw_b200.so")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+
+FILTER_WIDTHS = (3, 5, 7, 9, 11, 13, 15, 17)
+PLAIN_SOURCES = ("dwconv.cu", "resample.cu", "static_scratch.cu")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "-Xptxas=-v",
+]
+
+
+def _nvcc():
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found: libpdw_b200.so cannot be built on this machine")
+    return exe
+
+
+def _source_digest():
+    h = hashlib.sha256()
+    names = sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
+    for name in names + [os.path.join(INCLUDE, "pdw_b200.h")]:
+        path = name if os.path.isabs(name) else os.path.join(CSRC, name)
+        with open(path, "rb") as f:
+            h.update(name.encode())
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _jobs():
+    jobs = []
+    for src in PLAIN_SOURCES:
+        if os.path.exists(os.path.join(CSRC, src)):
+            jobs.append((src, [], os.path.join(OBJ_DIR, src.replace(".cu", ".o"))))
+    for k in FILTER_WIDTHS:
+        jobs.append(("dwconv_k.cu", ["-DPDW_K=%d" % k], os.path.join(OBJ_DIR, "dwconv_k%d.o" % k)))
+    return jobs
+
+
+def _compile(job, verbose):
+    src, defs, obj = job
+    cmd = [_nvcc()] + NVCC_FLAGS + defs + ["-I", INCLUDE, "-c", os.path.join(CSRC, src), "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc failed for %s %s:\n%s" % (src, " ".join(defs), r.stderr[-4000:]))
+    if verbose:
+        sys.stderr.write(r.stderr)
+    return obj, r.stderr
+
+
+def build(force=False, verbose=False):
+    """Compile and link the library if sources changed (or ``force``). Returns the library path."""
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    stamp = os.path.join(OBJ_DIR, "digest.txt")
+    digest = _source_digest()
+    if not force and os.path.exists(LIB_PATH) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == digest:
+                return LIB_PATH
+    jobs = _jobs()
+    logs = []
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+        for obj, log in pool.map(lambda j: _compile(j, verbose), jobs):
+            logs.append(log)
+    link = [_nvcc(), "-shared", "-o", LIB_PATH] + [j[2] for j in jobs] + ["-lcudart_static", "-ldl", "-lpthread", "-lrt"]
+    r = subprocess.run(link, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("link failed:\n" + r.stderr[-4000:])
+    with open(os.path.join(OBJ_DIR, "ptxas.log"), "w") as f:
+        f.write("\n".join(logs))
+    with open(stamp, "w") as f:
+        f.write(digest)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

@@ -1,0 +1,182 @@
+// Shared device/host helpers of libpdw_b200: element types, packed-pair arithmetic,
+// TMA + mbarrier wrappers (inline PTX for sm_100a) and the host-side error plumbing.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pdw_b200.h"
+
+namespace pdw {
+
+// ---------------------------------------------------------------------------------------------
+// Host-side error handling
+// ---------------------------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return PDW_ERR_CUDA;
+}
+
+#define PDW_CUDA_TRY(expr)                                   \
+    do {                                                     \
+        cudaError_t _e = (expr);                             \
+        if (_e != cudaSuccess) return ::pdw::cuda_fail(_e);  \
+    } while (0)
+
+inline int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e);
+    return PDW_OK;
+}
+
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline size_t dtype_size(int dtype) { return dtype == PDW_F32 ? 4 : 2; }
+inline bool dtype_ok(int dtype) { return dtype == PDW_F32 || dtype == PDW_F16 || dtype == PDW_BF16; }
+
+int sm_count();  // multiprocessors of the current device (cached per device)
+
+// Tuning knobs (see pdw_set_tuning).
+int tuning(int key);
+
+// Encodes a 4-D tiled tensor map over a dense NHWC tensor: dims (fastest first) {C, W, H, B},
+// box {box_c, box_w, box_h, 1}.  Out-of-range parts of a box read as zero, which is what gives
+// the convolution its zero padding without a single predicate in the kernels.
+int make_nhwc_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int W, int C,
+                         int box_c, int box_w, int box_h);
+
+// ---------------------------------------------------------------------------------------------
+// Element traits.  A "pair" is two adjacent channels: 32 bits for half/bfloat16, 64 for float.
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static constexpr int kDtype = PDW_F32;
+    using pair_t = float2;
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+    static __device__ __forceinline__ float2 unpack(float2 p) { return p; }
+    static __device__ __forceinline__ float2 pack(float2 f) { return f; }
+};
+template <> struct Elem<__half> {
+    static constexpr int kDtype = PDW_F16;
+    using pair_t = uint32_t;
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ float2 unpack(uint32_t p) {
+        return __half22float2(*reinterpret_cast<const __half2*>(&p));
+    }
+    static __device__ __forceinline__ uint32_t pack(float2 f) {
+        __half2 h = __float22half2_rn(f);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int kDtype = PDW_BF16;
+    using pair_t = uint32_t;
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float2 unpack(uint32_t p) {
+        // bf16 -> fp32 is a 16-bit shift: integer pipe, no conversion unit.
+        return make_float2(__uint_as_float(p << 16), __uint_as_float(p & 0xffff0000u));
+    }
+    static __device__ __forceinline__ uint32_t pack(float2 f) {
+        __nv_bfloat162 h = __float22bfloat162_rn(f);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+
+// acc += a * b on two packed fp32 lanes in one instruction (sm_100 FFMA2): halves the issue
+// slots the FMA stream needs, leaving the other half for shared-memory loads and conversions.
+__device__ __forceinline__ void ffma2(float2& acc, const float2 a, const float2 b) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%0, %1};\n\t"
+        "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t}"
+        : "+f"(acc.x), "+f"(acc.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+}
+
+// acc(fp32) += a(16-bit) * b(16-bit), product exact, one rounding: the sm_100 mixed-precision FMA.
+// Bitwise the same result as converting both operands to fp32 and using an fp32 FMA.
+template <typename T> __device__ __forceinline__ void fma_mixed(float2& acc, uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ void fma_mixed<__half>(float2& acc, uint32_t a, uint32_t b) {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\t"
+        "mov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, al, bl, %0;\n\t"
+        "fma.rn.f32.f16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc.x), "+f"(acc.y)
+        : "r"(a), "r"(b));
+}
+template <> __device__ __forceinline__ void fma_mixed<__nv_bfloat16>(float2& acc, uint32_t a, uint32_t b) {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\t"
+        "mov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, al, bl, %0;\n\t"
+        "fma.rn.f32.bf16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc.x), "+f"(acc.y)
+        : "r"(a), "r"(b));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shared-memory barriers and TMA (cp.async.bulk.tensor), plain per-CTA form: no cluster multicast.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Waits for the given phase of a barrier, but never forever: after ~2^31 clock ticks (about a
+// second) it gives up, records PDW_ERR_DEVICE_TIMEOUT in *status_word (if any) and returns false
+// so that the caller can leave the kernel with the context intact.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int32_t* status_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > (1ll << 31)) {
+            if (status_word) atomicExch(status_word, PDW_ERR_DEVICE_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ __forceinline__ int round_up(int a, int b) { return ceil_div(a, b) * b; }
+
+}  // namespace pdw

@@ -1,0 +1,362 @@
+// Entry points of the depthwise convolution (forward, input gradient, weight/bias gradient),
+// the untiled kernels that cover every stride / dilation / padding / channel count, and the
+// library-wide helpers (tensor-map encoding, tuning knobs, status strings).
+#include <mutex>
+
+#include "dwconv_tiled.cuh"
+
+namespace pdw {
+
+thread_local int g_last_cuda_error = 0;
+
+// ---------------------------------------------------------------------------------------------
+// Library-wide helpers
+// ---------------------------------------------------------------------------------------------
+static int g_tuning[3] = {0, 16, 0};
+int tuning(int key) { return g_tuning[key]; }
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn get_encode_fn() {
+    static encode_tiled_fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_tiled_fn>(p);
+    });
+    return fn;
+}
+
+int make_nhwc_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int W, int C, int box_c,
+                         int box_w, int box_h) {
+    encode_tiled_fn fn = get_encode_fn();
+    if (fn == nullptr) return cuda_fail(cudaErrorSymbolNotFound);
+    const size_t es = dtype_size(dtype);
+    const CUtensorMapDataType dt = dtype == PDW_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : dtype == PDW_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)C * es, (cuuint64_t)W * C * es, (cuuint64_t)H * W * C * es};
+    const cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)box_w, (cuuint32_t)box_h, 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = 100000 + (int)r;   // driver error space, kept apart from cudaError_t
+        return PDW_ERR_CUDA;
+    }
+    return PDW_OK;
+}
+
+extern const KernelSet kernel_set_k3, kernel_set_k5, kernel_set_k7, kernel_set_k9, kernel_set_k11, kernel_set_k13,
+    kernel_set_k15, kernel_set_k17;
+
+const KernelSet* find_kernel_set(int kw) {
+    switch (kw) {
+        case 3: return &kernel_set_k3;
+        case 5: return &kernel_set_k5;
+        case 7: return &kernel_set_k7;
+        case 9: return &kernel_set_k9;
+        case 11: return &kernel_set_k11;
+        case 13: return &kernel_set_k13;
+        case 15: return &kernel_set_k15;
+        case 17: return &kernel_set_k17;
+    }
+    return nullptr;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Untiled kernels: one thread per output element, channel fastest (coalesced).  They define the
+// operation for every parameter combination; the tiled kernels take over where they apply.
+// ---------------------------------------------------------------------------------------------
+struct Geom {
+    int B, H, W, C, OH, OW, KH, KW, sh, sw, ph, pw, dh, dw;
+};
+
+template <typename T>
+__global__ void dwconv_fwd_direct_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                                         T* __restrict__ y, const Geom g, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int c = (int)(idx % g.C);
+    long long t = idx / g.C;
+    const int ow = (int)(t % g.OW);  t /= g.OW;
+    const int oh = (int)(t % g.OH);
+    const int b = (int)(t / g.OH);
+    float acc = bias ? Elem<T>::to_f(bias[c]) : 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+        const int ih = oh * g.sh - g.ph + kh * g.dh;
+        if (ih < 0 || ih >= g.H) continue;
+        for (int kw = 0; kw < g.KW; ++kw) {
+            const int iw = ow * g.sw - g.pw + kw * g.dw;
+            if (iw < 0 || iw >= g.W) continue;
+            acc = fmaf(Elem<T>::to_f(x[(((size_t)b * g.H + ih) * g.W + iw) * g.C + c]),
+                       Elem<T>::to_f(w[((size_t)kh * g.KW + kw) * g.C + c]), acc);
+        }
+    }
+    y[idx] = Elem<T>::from_f(acc);
+}
+
+// dx[b,ih,iw,c] = sum over taps with (ih + p - kh*d) divisible by s and in range of gout * w.
+template <typename T>
+__global__ void dwconv_bwd_input_direct_kernel(const T* __restrict__ gout, const T* __restrict__ w, T* __restrict__ dx,
+                                               const Geom g, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int c = (int)(idx % g.C);
+    long long t = idx / g.C;
+    const int iw = (int)(t % g.W);  t /= g.W;
+    const int ih = (int)(t % g.H);
+    const int b = (int)(t / g.H);
+    float acc = 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+        const int nh = ih + g.ph - kh * g.dh;
+        if (nh < 0 || nh % g.sh != 0) continue;
+        const int oh = nh / g.sh;
+        if (oh >= g.OH) continue;
+        for (int kw = 0; kw < g.KW; ++kw) {
+            const int nw = iw + g.pw - kw * g.dw;
+            if (nw < 0 || nw % g.sw != 0) continue;
+            const int ow = nw / g.sw;
+            if (ow >= g.OW) continue;
+            acc = fmaf(Elem<T>::to_f(gout[(((size_t)b * g.OH + oh) * g.OW + ow) * g.C + c]),
+                       Elem<T>::to_f(w[((size_t)kh * g.KW + kw) * g.C + c]), acc);
+        }
+    }
+    dx[idx] = Elem<T>::from_f(acc);
+}
+
+// One block per (tap, 32-channel group); 8 pixel lanes x 32 channels, fixed-order tree in shared
+// memory.  blockIdx.x == KH*KW is the bias "tap".
+template <typename T>
+__global__ void dwconv_bwd_weight_direct_kernel(const T* __restrict__ x, const T* __restrict__ gout, void* dw,
+                                                void* dbias, const Geom g, int out_fp32) {
+    __shared__ float red[8][32];
+    const int tap = blockIdx.x;
+    const bool is_bias = tap == g.KH * g.KW;
+    const int kh = is_bias ? 0 : tap / g.KW, kw = is_bias ? 0 : tap % g.KW;
+    const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
+    const int c = blockIdx.y * 32 + cl;
+    float acc = 0.f;
+    if (c < g.C) {
+        const long long npix = (long long)g.B * g.OH * g.OW;
+        for (long long pix = pl; pix < npix; pix += 8) {
+            const int ow = (int)(pix % g.OW);
+            const int oh = (int)((pix / g.OW) % g.OH);
+            const int b = (int)(pix / ((long long)g.OW * g.OH));
+            const float gv = Elem<T>::to_f(gout[(size_t)pix * g.C + c]);
+            if (is_bias) {
+                acc += gv;
+            } else {
+                const int ih = oh * g.sh - g.ph + kh * g.dh, iw = ow * g.sw - g.pw + kw * g.dw;
+                if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
+                    acc = fmaf(gv, Elem<T>::to_f(x[(((size_t)b * g.H + ih) * g.W + iw) * g.C + c]), acc);
+            }
+        }
+    }
+    red[pl][cl] = acc;
+    __syncthreads();
+    if (pl == 0 && c < g.C) {
+        float sum = 0.f;
+        for (int i = 0; i < 8; ++i) sum += red[i][cl];
+        void* dst = is_bias ? dbias : dw;
+        const size_t e = is_bias ? (size_t)c : ((size_t)kh * g.KW + kw) * g.C + c;
+        if (out_fp32) static_cast<float*>(dst)[e] = sum; else static_cast<T*>(dst)[e] = Elem<T>::from_f(sum);
+    }
+}
+
+static int check_geom(const pdw_conv_geom* g, Geom* o) {
+    if (g == nullptr) return PDW_ERR_NULL_POINTER;
+    if (g->batch <= 0 || g->in_h <= 0 || g->in_w <= 0 || g->channels <= 0 || g->kernel_h <= 0 || g->kernel_w <= 0 ||
+        g->stride_h <= 0 || g->stride_w <= 0 || g->dil_h <= 0 || g->dil_w <= 0 || g->pad_h < 0 || g->pad_w < 0)
+        return PDW_ERR_BAD_SHAPE;
+    const int oh = pdw_conv_out_size(g->in_h, g->kernel_h, g->stride_h, g->pad_h, g->dil_h);
+    const int ow = pdw_conv_out_size(g->in_w, g->kernel_w, g->stride_w, g->pad_w, g->dil_w);
+    if (oh <= 0 || ow <= 0) return PDW_ERR_BAD_SHAPE;
+    *o = Geom{g->batch, g->in_h, g->in_w, g->channels, oh, ow, g->kernel_h, g->kernel_w, g->stride_h, g->stride_w,
+              g->pad_h, g->pad_w, g->dil_h, g->dil_w};
+    return PDW_OK;
+}
+
+// The tiled kernels need stride 1, dilation 1, channel rows that TMA can address (16-byte
+// multiples) and 16-byte aligned bases.
+static bool tiled_applies(const Geom& g, int dtype, const void* a, const void* b) {
+    if (tuning(2)) return false;
+    if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1) return false;
+    if (((size_t)g.C * dtype_size(dtype)) % 16 != 0) return false;
+    if (!aligned_to(a, 16) || (b != nullptr && !aligned_to(b, 16))) return false;
+    if (g.KH > 32) return false;
+    return find_kernel_set(g.KW) != nullptr;
+}
+
+template <typename T>
+static int fwd_direct(const void* x, const void* w, const void* bias, void* y, const Geom& g, cudaStream_t st) {
+    const long long total = (long long)g.B * g.OH * g.OW * g.C;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return PDW_ERR_BAD_SHAPE;
+    dwconv_fwd_direct_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(w),
+                                                                  static_cast<const T*>(bias), static_cast<T*>(y), g,
+                                                                  total);
+    return check_launch();
+}
+template <typename T>
+static int bwd_input_direct(const void* go, const void* w, void* dx, const Geom& g, cudaStream_t st) {
+    const long long total = (long long)g.B * g.H * g.W * g.C;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return PDW_ERR_BAD_SHAPE;
+    dwconv_bwd_input_direct_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const T*>(go), static_cast<const T*>(w), static_cast<T*>(dx), g, total);
+    return check_launch();
+}
+template <typename T>
+static int bwd_weight_direct(const void* x, const void* go, void* dw, void* dbias, const Geom& g, int out_fp32,
+                             cudaStream_t st) {
+    dim3 grid(g.KH * g.KW + (dbias ? 1 : 0), ceil_div(g.C, 32));
+    dwconv_bwd_weight_direct_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(go), dw,
+                                                             dbias, g, out_fp32);
+    return check_launch();
+}
+
+#define PDW_DISPATCH_DTYPE(dtype, CALL)                         \
+    switch (dtype) {                                            \
+        case PDW_F32: { using T = float; return CALL; }         \
+        case PDW_F16: { using T = __half; return CALL; }        \
+        case PDW_BF16: { using T = __nv_bfloat16; return CALL; } \
+        default: return PDW_ERR_BAD_DTYPE;                      \
+    }
+
+}  // namespace pdw
+
+using namespace pdw;
+
+extern "C" {
+
+int pdw_version(void) { return 100; }
+
+const char* pdw_status_string(int status) {
+    switch (status) {
+        case PDW_OK: return "ok";
+        case PDW_ERR_NULL_POINTER: return "null pointer argument";
+        case PDW_ERR_BAD_DTYPE: return "dtype must be PDW_F32, PDW_F16 or PDW_BF16";
+        case PDW_ERR_BAD_SHAPE: return "bad shape: non-positive extent, empty output or too many elements";
+        case PDW_ERR_UNSUPPORTED: return "parameter combination not supported by this entry point";
+        case PDW_ERR_WORKSPACE: return "workspace missing or smaller than the size the query function returns";
+        case PDW_ERR_MISALIGNED: return "pointer not aligned to the element size (workspace: 16 bytes)";
+        case PDW_ERR_CUDA: return "a CUDA call failed (see pdw_last_cuda_error)";
+        case PDW_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        case PDW_ERR_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
+    }
+    return "unknown status";
+}
+
+int pdw_last_cuda_error(void) { return g_last_cuda_error; }
+
+int pdw_set_tuning(int key, int value) {
+    if (key < 0 || key > 2) return -1;
+    if (key == 1 && value != 16 && value != 32) return -1;
+    const int prev = g_tuning[key];
+    g_tuning[key] = value;
+    return prev;
+}
+
+int pdw_conv_out_size(int in, int kernel, int stride, int pad, int dil) {
+    if (stride <= 0) return 0;
+    const int num = in + 2 * pad - dil * (kernel - 1) - 1;
+    if (num < 0) return 0;
+    return num / stride + 1;
+}
+
+int pdw_dwconv_fwd(const void* x, const void* w, const void* bias, void* y, const pdw_conv_geom* geom, int dtype,
+                   int32_t* status_word, void* stream) {
+    if (!x || !w || !y) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    Geom g;
+    int rc = check_geom(geom, &g);
+    if (rc != PDW_OK) return rc;
+    const size_t es = dtype_size(dtype);
+    if (!aligned_to(x, es) || !aligned_to(w, es) || !aligned_to(y, es) || (bias && !aligned_to(bias, es)))
+        return PDW_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tiled_applies(g, dtype, x, y) && aligned_to(w, 2 * es) && (!bias || aligned_to(bias, 2 * es))) {
+        TiledArgs a{x, w, bias, y, g.B, g.H, g.W, g.C, g.OH, g.OW, g.KH, g.KW, g.ph, g.pw, 0, dtype, status_word, st};
+        rc = find_kernel_set(g.KW)->tiled(a);
+        if (rc != PDW_ERR_UNSUPPORTED) return rc;
+    }
+    PDW_DISPATCH_DTYPE(dtype, fwd_direct<T>(x, w, bias, y, g, st));
+}
+
+int pdw_dwconv_bwd_input(const void* grad_out, const void* w, void* dx, const pdw_conv_geom* geom, int dtype,
+                         int32_t* status_word, void* stream) {
+    if (!grad_out || !w || !dx) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    Geom g;
+    int rc = check_geom(geom, &g);
+    if (rc != PDW_OK) return rc;
+    const size_t es = dtype_size(dtype);
+    if (!aligned_to(grad_out, es) || !aligned_to(w, es) || !aligned_to(dx, es)) return PDW_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Stride 1, dilation 1: dx is a correlation of grad_out [OH,OW] with the mirrored filter and
+    // padding K-1-p (must not be negative), producing exactly [in_h,in_w].
+    if (tiled_applies(g, dtype, grad_out, dx) && aligned_to(w, 2 * es) && g.KH - 1 - g.ph >= 0 &&
+        g.KW - 1 - g.pw >= 0) {
+        TiledArgs a{grad_out, w, nullptr, dx, g.B, g.OH, g.OW, g.C, g.H, g.W, g.KH, g.KW,
+                    g.KH - 1 - g.ph, g.KW - 1 - g.pw, 1, dtype, status_word, st};
+        rc = find_kernel_set(g.KW)->tiled(a);
+        if (rc != PDW_ERR_UNSUPPORTED) return rc;
+    }
+    PDW_DISPATCH_DTYPE(dtype, bwd_input_direct<T>(grad_out, w, dx, g, st));
+}
+
+size_t pdw_dwconv_bwd_weight_workspace(const pdw_conv_geom* geom, int dtype) {
+    Geom g;
+    if (!dtype_ok(dtype) || check_geom(geom, &g) != PDW_OK) return 0;
+    if (tuning(2) || g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1 || g.KH != g.KW) return 0;
+    if (((size_t)g.C * dtype_size(dtype)) % 16 != 0) return 0;
+    const KernelSet* ks = find_kernel_set(g.KW);
+    if (ks == nullptr) return 0;
+    return ks->wgrad_workspace(g.B, g.OH, g.OW, g.C, g.KH, dtype);
+}
+
+int pdw_dwconv_bwd_weight(const void* x, const void* grad_out, void* dw, void* dbias, const pdw_conv_geom* geom,
+                          int dtype, int out_fp32, void* workspace, size_t workspace_bytes, int32_t* status_word,
+                          void* stream) {
+    if (!x || !grad_out || !dw) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    Geom g;
+    int rc = check_geom(geom, &g);
+    if (rc != PDW_OK) return rc;
+    const size_t es = dtype_size(dtype), os = out_fp32 ? 4 : es;
+    if (!aligned_to(x, es) || !aligned_to(grad_out, es) || !aligned_to(dw, os) || (dbias && !aligned_to(dbias, os)))
+        return PDW_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t need = pdw_dwconv_bwd_weight_workspace(geom, dtype);
+    if (need > 0 && tiled_applies(g, dtype, x, grad_out)) {
+        if (workspace == nullptr || workspace_bytes < need) return PDW_ERR_WORKSPACE;
+        if (!aligned_to(workspace, 16)) return PDW_ERR_MISALIGNED;
+        WgradArgs a{x, grad_out, dw, dbias, g.B, g.H, g.W, g.C, g.OH, g.OW, g.KH, g.KW, g.ph, g.pw,
+                    dtype, out_fp32, workspace, workspace_bytes, status_word, st};
+        rc = find_kernel_set(g.KW)->wgrad(a);
+        if (rc != PDW_ERR_UNSUPPORTED) return rc;
+    }
+    PDW_DISPATCH_DTYPE(dtype, bwd_weight_direct<T>(x, grad_out, dw, dbias, g, out_fp32, st));
+}
+
+}  // extern "C"

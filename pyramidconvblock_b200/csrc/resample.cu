@@ -1,0 +1,337 @@
+// Bandwidth-bound companions of the convolution: adaptive average pool, bilinear resize and the
+// SimpleGate product, forward and backward.  One thread handles one 16-byte channel vector of one
+// pixel (8 half/bfloat16 or 4 float channels) so that every global access is a full 128-bit,
+// channel-contiguous transaction; tensors whose channel count or base address rules that out use the
+// one-element instantiation of the same kernels.  All backward kernels are gathers: each gradient
+// element is written exactly once, without atomics and without a preceding zero fill.
+#include "common.cuh"
+
+namespace pdw {
+
+template <typename T, int V> struct alignas(sizeof(T) * V) Vec { T v[V]; };
+
+template <typename T, int V>
+__device__ __forceinline__ void load_acc(const T* p, float (&acc)[V], float scale) {
+    const Vec<T, V> d = *reinterpret_cast<const Vec<T, V>*>(p);
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = fmaf(Elem<T>::to_f(d.v[i]), scale, acc[i]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_vec(T* p, const float (&acc)[V]) {
+    Vec<T, V> d;
+#pragma unroll
+    for (int i = 0; i < V; ++i) d.v[i] = Elem<T>::from_f(acc[i]);
+    *reinterpret_cast<Vec<T, V>*>(p) = d;
+}
+
+__device__ __forceinline__ int win_start(int o, int in, int out) { return (int)(((long long)o * in) / out); }
+__device__ __forceinline__ int win_end(int o, int in, int out) {
+    return (int)((((long long)o + 1) * in + out - 1) / out);
+}
+
+struct Shape { int B, H, W, C, OH, OW; };   // H,W: larger-index "input" of the forward op
+
+// ---- adaptive average pool ------------------------------------------------------------------
+template <typename T, int V>
+__global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int cv = s.C / V;
+    const int c = (int)(idx % cv) * V;
+    long long t = idx / cv;
+    const int ow = (int)(t % s.OW);  t /= s.OW;
+    const int oh = (int)(t % s.OH);
+    const int b = (int)(t / s.OH);
+    const int hs = win_start(oh, s.H, s.OH), he = win_end(oh, s.H, s.OH);
+    const int ws = win_start(ow, s.W, s.OW), we = win_end(ow, s.W, s.OW);
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    for (int ih = hs; ih < he; ++ih) {
+        const T* row = x + (((size_t)b * s.H + ih) * s.W) * s.C + c;
+        for (int iw = ws; iw < we; ++iw) load_acc<T, V>(row + (size_t)iw * s.C, acc, 1.f);
+    }
+    const float inv = 1.f / (float)((he - hs) * (we - ws));
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] *= inv;
+    store_vec<T, V>(y + (size_t)idx * V, acc);
+}
+
+// dx[ih,iw] = sum over the outputs whose window holds (ih,iw) of grad_out / window area.  The
+// outputs that hold input index i are exactly [floor(i*out/in), ceil((i+1)*out/in)).
+template <typename T, int V>
+__global__ void pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int cv = s.C / V;
+    const int c = (int)(idx % cv) * V;
+    long long t = idx / cv;
+    const int iw = (int)(t % s.W);  t /= s.W;
+    const int ih = (int)(t % s.H);
+    const int b = (int)(t / s.H);
+    const int oh0 = win_start(ih, s.OH, s.H), oh1 = win_end(ih, s.OH, s.H);
+    const int ow0 = win_start(iw, s.OW, s.W), ow1 = win_end(iw, s.OW, s.W);
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    for (int oh = oh0; oh < oh1; ++oh) {
+        const int kh = win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH);
+        const T* row = go + (((size_t)b * s.OH + oh) * s.OW) * s.C + c;
+        for (int ow = ow0; ow < ow1; ++ow) {
+            const int kw = win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW);
+            load_acc<T, V>(row + (size_t)ow * s.C, acc, 1.f / (float)(kh * kw));
+        }
+    }
+    store_vec<T, V>(dx + (size_t)idx * V, acc);
+}
+
+// ---- bilinear resize (align_corners = False) ---------------------------------------------------
+struct Tap { int i0, i1; float l0, l1; };
+__device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
+    float src = scale * ((float)dst + 0.5f) - 0.5f;
+    src = src < 0.f ? 0.f : src;
+    int i0 = (int)src;
+    i0 = i0 > in - 1 ? in - 1 : i0;
+    Tap t;
+    t.i0 = i0;
+    t.i1 = i0 < in - 1 ? i0 + 1 : i0;
+    t.l1 = src - (float)i0;
+    t.l0 = 1.f - t.l1;
+    return t;
+}
+
+// s.H,s.W: source extent (small), s.OH,s.OW: destination extent.
+template <typename T, int V>
+__global__ void upsample_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s, float scale_h,
+                                    float scale_w, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int cv = s.C / V;
+    const int c = (int)(idx % cv) * V;
+    long long t = idx / cv;
+    const int ow = (int)(t % s.OW);  t /= s.OW;
+    const int oh = (int)(t % s.OH);
+    const int b = (int)(t / s.OH);
+    const Tap ty = source_taps(oh, scale_h, s.H), tx = source_taps(ow, scale_w, s.W);
+    const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C + c;
+    const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C + c;
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    load_acc<T, V>(r0 + (size_t)tx.i0 * s.C, acc, ty.l0 * tx.l0);
+    load_acc<T, V>(r0 + (size_t)tx.i1 * s.C, acc, ty.l0 * tx.l1);
+    load_acc<T, V>(r1 + (size_t)tx.i0 * s.C, acc, ty.l1 * tx.l0);
+    load_acc<T, V>(r1 + (size_t)tx.i1 * s.C, acc, ty.l1 * tx.l1);
+    store_vec<T, V>(y + (size_t)idx * V, acc);
+}
+
+// Weight with which destination index `dst` reads source index `i` (0 if it does not).
+__device__ __forceinline__ float tap_weight(int dst, int i, float scale, int in) {
+    const Tap t = source_taps(dst, scale, in);
+    return (t.i0 == i ? t.l0 : 0.f) + (t.i1 == i ? t.l1 : 0.f);
+}
+// Destination indices that can read source index i: src(dst) in (i-1, i+1), widened by one on each
+// side against rounding, clamped to the valid range.
+__device__ __forceinline__ void dst_range(int i, float scale, int out, int* lo, int* hi) {
+    const float inv = 1.f / scale;
+    int a = (int)floorf(((float)i - 1.f + 0.5f) * inv - 0.5f) - 1;
+    int b = (int)ceilf(((float)i + 1.f + 0.5f) * inv - 0.5f) + 1;
+    *lo = a < 0 ? 0 : a;
+    *hi = b > out - 1 ? out - 1 : b;
+}
+
+template <typename T, int V>
+__global__ void upsample_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s, float scale_h,
+                                    float scale_w, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int cv = s.C / V;
+    const int c = (int)(idx % cv) * V;
+    long long t = idx / cv;
+    const int ix = (int)(t % s.W);  t /= s.W;
+    const int iy = (int)(t % s.H);
+    const int b = (int)(t / s.H);
+    int oy0, oy1, ox0, ox1;
+    dst_range(iy, scale_h, s.OH, &oy0, &oy1);
+    dst_range(ix, scale_w, s.OW, &ox0, &ox1);
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    for (int oy = oy0; oy <= oy1; ++oy) {
+        const float wy = tap_weight(oy, iy, scale_h, s.H);
+        if (wy == 0.f) continue;
+        const T* row = go + (((size_t)b * s.OH + oy) * s.OW) * s.C + c;
+        for (int ox = ox0; ox <= ox1; ++ox) {
+            const float wx = tap_weight(ox, ix, scale_w, s.W);
+            if (wx == 0.f) continue;
+            load_acc<T, V>(row + (size_t)ox * s.C, acc, wy * wx);
+        }
+    }
+    store_vec<T, V>(dx + (size_t)idx * V, acc);
+}
+
+// ---- gate ----------------------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void gate_fwd_kernel(const T* __restrict__ a, T* __restrict__ y, int C, float inv_scale,
+                                const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int hv = (C / 2) / V;
+    const int j = (int)(idx % hv) * V;
+    const long long n = idx / hv;
+    const Vec<T, V> x1 = *reinterpret_cast<const Vec<T, V>*>(a + (size_t)n * C + j);
+    const Vec<T, V> x2 = *reinterpret_cast<const Vec<T, V>*>(a + (size_t)n * C + C / 2 + j);
+    float r[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) r[i] = Elem<T>::to_f(x1.v[i]) * (Elem<T>::to_f(x2.v[i]) * inv_scale);
+    store_vec<T, V>(y + (size_t)n * (C / 2) + j, r);
+}
+
+template <typename T, int V>
+__global__ void gate_bwd_kernel(const T* __restrict__ a, const T* __restrict__ gy, T* __restrict__ ga, int C,
+                                float inv_scale, const long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int hv = (C / 2) / V;
+    const int j = (int)(idx % hv) * V;
+    const long long n = idx / hv;
+    const Vec<T, V> x1 = *reinterpret_cast<const Vec<T, V>*>(a + (size_t)n * C + j);
+    const Vec<T, V> x2 = *reinterpret_cast<const Vec<T, V>*>(a + (size_t)n * C + C / 2 + j);
+    const Vec<T, V> g = *reinterpret_cast<const Vec<T, V>*>(gy + (size_t)n * (C / 2) + j);
+    float r1[V], r2[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const float gs = Elem<T>::to_f(g.v[i]) * inv_scale;
+        r1[i] = gs * Elem<T>::to_f(x2.v[i]);
+        r2[i] = gs * Elem<T>::to_f(x1.v[i]);
+    }
+    store_vec<T, V>(ga + (size_t)n * C + j, r1);
+    store_vec<T, V>(ga + (size_t)n * C + C / 2 + j, r2);
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+static int check_shape(int B, int H, int W, int C, int OH, int OW) {
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || OH <= 0 || OW <= 0) return PDW_ERR_BAD_SHAPE;
+    return PDW_OK;
+}
+// 16-byte vectors when the channel run and every base address allow it, else single elements.
+static inline int vec_width(int dtype, int c_units, const void* a, const void* b, const void* c = nullptr) {
+    const int v = 16 / (int)dtype_size(dtype);
+    if (c_units % v != 0) return 1;
+    if (!aligned_to(a, 16) || !aligned_to(b, 16) || (c && !aligned_to(c, 16))) return 1;
+    return v;
+}
+static inline bool grid_for(long long total, unsigned* blocks) {
+    const long long n = (total + 255) / 256;
+    if (n <= 0 || n > 0x7fffffffLL) return false;
+    *blocks = (unsigned)n;
+    return true;
+}
+
+template <int V> struct Width { static constexpr int value = V; };
+// Calls f(T{}, Width<V>{}) with the element type of `dtype` and the vector width `v` as types.
+template <typename F>
+static int with_type_and_width(int dtype, int v, F&& f) {
+    switch (dtype) {
+        case PDW_F32: return v > 1 ? f(float{}, Width<4>{}) : f(float{}, Width<1>{});
+        case PDW_F16: return v > 1 ? f(__half{}, Width<8>{}) : f(__half{}, Width<1>{});
+        case PDW_BF16: return v > 1 ? f(__nv_bfloat16{}, Width<8>{}) : f(__nv_bfloat16{}, Width<1>{});
+    }
+    return PDW_ERR_BAD_DTYPE;
+}
+
+enum class Resample { PoolFwd, PoolBwd, UpFwd, UpBwd };
+
+// Shared argument checking + launch of the four spatial resampling kernels.  `src`/`dst` are the
+// tensors read and written; (H,W) is the forward op's input extent, (OH,OW) its output extent.
+template <Resample OP>
+static int run_resample(const void* src, void* dst, int B, int H, int W, int C, int OH, int OW, int dtype,
+                        void* stream) {
+    if (!src || !dst) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    const int rc = check_shape(B, H, W, C, OH, OW);
+    if (rc) return rc;
+    if (!aligned_to(src, dtype_size(dtype)) || !aligned_to(dst, dtype_size(dtype))) return PDW_ERR_MISALIGNED;
+    const int v = vec_width(dtype, C, src, dst);
+    constexpr bool writes_small = (OP == Resample::PoolFwd || OP == Resample::UpBwd);
+    constexpr bool pool = (OP == Resample::PoolFwd || OP == Resample::PoolBwd);
+    // Pool: (H,W) is the big side.  Upsample: (H,W) is the small side.  One thread per written vector.
+    const bool dst_is_hw = pool ? !writes_small : writes_small;
+    const long long total = (long long)B * (dst_is_hw ? (long long)H * W : (long long)OH * OW) * (C / v);
+    unsigned blocks;
+    if (!grid_for(total, &blocks)) return PDW_ERR_BAD_SHAPE;
+    const Shape s{B, H, W, C, OH, OW};
+    const float sh = (float)H / (float)OH, sw = (float)W / (float)OW;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return with_type_and_width(dtype, v, [&](auto t, auto w) {
+        using T = decltype(t);
+        constexpr int V = decltype(w)::value;
+        const T* in = static_cast<const T*>(src);
+        T* out = static_cast<T*>(dst);
+        if constexpr (OP == Resample::PoolFwd) pool_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, total);
+        else if constexpr (OP == Resample::PoolBwd) pool_bwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, total);
+        else if constexpr (OP == Resample::UpFwd) upsample_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, sh, sw, total);
+        else upsample_bwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, sh, sw, total);
+        return check_launch();
+    });
+}
+
+}  // namespace pdw
+
+using namespace pdw;
+
+extern "C" {
+
+int pdw_pool_fwd(const void* x, void* y, int B, int H, int W, int C, int OH, int OW, int dtype, void* stream) {
+    return run_resample<Resample::PoolFwd>(x, y, B, H, W, C, OH, OW, dtype, stream);
+}
+int pdw_pool_bwd(const void* go, void* dx, int B, int H, int W, int C, int OH, int OW, int dtype, void* stream) {
+    return run_resample<Resample::PoolBwd>(go, dx, B, H, W, C, OH, OW, dtype, stream);
+}
+int pdw_upsample_fwd(const void* x, void* y, int B, int H, int W, int C, int OH, int OW, int dtype, void* stream) {
+    return run_resample<Resample::UpFwd>(x, y, B, H, W, C, OH, OW, dtype, stream);
+}
+int pdw_upsample_bwd(const void* go, void* dx, int B, int H, int W, int C, int OH, int OW, int dtype, void* stream) {
+    return run_resample<Resample::UpBwd>(go, dx, B, H, W, C, OH, OW, dtype, stream);
+}
+
+int pdw_gate_fwd(const void* a, void* y, int64_t pixels, int C, float inv_scale, int dtype, void* stream) {
+    if (!a || !y) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    if (pixels <= 0 || C <= 0 || (C % 2) != 0) return PDW_ERR_BAD_SHAPE;
+    if (!aligned_to(a, dtype_size(dtype)) || !aligned_to(y, dtype_size(dtype))) return PDW_ERR_MISALIGNED;
+    const int v = vec_width(dtype, C / 2, a, y);
+    const long long total = (long long)pixels * ((C / 2) / v);
+    unsigned blocks;
+    if (!grid_for(total, &blocks)) return PDW_ERR_BAD_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return with_type_and_width(dtype, v, [&](auto t, auto w) {
+        using T = decltype(t);
+        constexpr int V = decltype(w)::value;
+        gate_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(static_cast<const T*>(a), static_cast<T*>(y), C, inv_scale, total);
+        return check_launch();
+    });
+}
+
+int pdw_gate_bwd(const void* a, const void* gy, void* ga, int64_t pixels, int C, float inv_scale, int dtype,
+                 void* stream) {
+    if (!a || !gy || !ga) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    if (pixels <= 0 || C <= 0 || (C % 2) != 0) return PDW_ERR_BAD_SHAPE;
+    const size_t es = dtype_size(dtype);
+    if (!aligned_to(a, es) || !aligned_to(gy, es) || !aligned_to(ga, es)) return PDW_ERR_MISALIGNED;
+    const int v = vec_width(dtype, C / 2, a, gy, ga);
+    const long long total = (long long)pixels * ((C / 2) / v);
+    unsigned blocks;
+    if (!grid_for(total, &blocks)) return PDW_ERR_BAD_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return with_type_and_width(dtype, v, [&](auto t, auto w) {
+        using T = decltype(t);
+        constexpr int V = decltype(w)::value;
+        gate_bwd_kernel<T, V><<<blocks, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(gy),
+                                                      static_cast<T*>(ga), C, inv_scale, total);
+        return check_launch();
+    });
+}
+
+}  // extern "C"

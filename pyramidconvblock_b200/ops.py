@@ -1,0 +1,324 @@
+"""Tensor-level wrappers and autograd Functions over the C-ABI library.
+
+The Functions keep the reference's names and call signatures
+(pyramid_dwconv/dwconv_triton.py:299-387, pyramid_dwconv/avgpool_triton.py:205-257); the work
+itself happens in hand-written sm_100a kernels.  Everything here requires CUDA tensors: there is
+no CPU implementation to fall back to.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.PDW_F32, torch.float16: _lib.PDW_F16, torch.bfloat16: _lib.PDW_BF16}
+_status_words = {}
+
+
+def _dtype_code(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError("pyramid_dwconv kernels support float32, float16 and bfloat16, got %s" % t.dtype)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "pyramid_dwconv kernels run on CUDA devices only (got a %s tensor); there is no CPU fallback"
+                % t.device.type)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _pair(v):
+    if isinstance(v, (tuple, list)):
+        if len(v) != 2:
+            raise ValueError("expected an int or a pair, got %r" % (v,))
+        return int(v[0]), int(v[1])
+    return int(v), int(v)
+
+
+def status_word(device):
+    """Per-device int32 the kernels set when one of their bounded barrier waits runs out."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+        _status_words[key] = w
+    return w
+
+
+def check_device_status(device=None):
+    """Synchronises and raises if any kernel launched so far reported a timed-out wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        _lib.check(v, "a pyramid_dwconv kernel")
+
+
+def _geom(x_shape, k, stride, padding, dilation):
+    B, H, W, C = x_shape
+    return _lib.ConvGeom(B, H, W, C, k[0], k[1], stride[0], stride[1], padding[0], padding[1], dilation[0],
+                         dilation[1])
+
+
+def conv_out_hw(H, W, k, stride, padding, dilation):
+    """Output extent, the formula of pyramid_dwconv/dwconv_triton.py:311-312."""
+    L = _lib.lib()
+    return (L.pdw_conv_out_size(H, k[0], stride[0], padding[0], dilation[0]),
+            L.pdw_conv_out_size(W, k[1], stride[1], padding[1], dilation[1]))
+
+
+def _check_nhwc(x, name):
+    if x.dim() != 4:
+        raise RuntimeError("%s must be a 4-D [B,H,W,C] tensor, got %d-D" % (name, x.dim()))
+
+
+def dwconv_forward(x, weight, bias=None, stride=1, padding=0, dilation=1):
+    """y[B,OH,OW,C] = depthwise correlation of x[B,H,W,C] with weight[KH,KW,C] (+ bias[C])."""
+    _require_cuda(x, weight, bias)
+    _check_nhwc(x, "input")
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    if weight.dim() != 3 or weight.shape[2] != x.shape[3]:
+        raise RuntimeError("weight must be [KH,KW,C] with C == input channels")
+    if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise RuntimeError("input, weight and bias must share one dtype")
+    x, weight = x.contiguous(), weight.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    B, H, W, C = x.shape
+    k = (weight.shape[0], weight.shape[1])
+    OH, OW = conv_out_hw(H, W, k, stride, padding, dilation)
+    if OH <= 0 or OW <= 0:
+        raise RuntimeError("convolution output would be empty")
+    y = torch.empty((B, OH, OW, C), device=x.device, dtype=x.dtype)
+    g = _geom(x.shape, k, stride, padding, dilation)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().pdw_dwconv_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), ctypes.byref(g), _dtype_code(x),
+                                       _ptr(status_word(x.device)), _stream(x))
+    _lib.check(rc, "pdw_dwconv_fwd")
+    return y
+
+
+def dwconv_backward_input(grad_out, weight, input_hw, stride=1, padding=0, dilation=1):
+    """dx[B,H,W,C] for the convolution whose input extent was input_hw."""
+    _require_cuda(grad_out, weight)
+    _check_nhwc(grad_out, "grad_output")
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    grad_out, weight = grad_out.contiguous(), weight.contiguous()
+    B, OH, OW, C = grad_out.shape
+    H, W = input_hw
+    k = (weight.shape[0], weight.shape[1])
+    if conv_out_hw(H, W, k, stride, padding, dilation) != (OH, OW):
+        raise RuntimeError("grad_output extent does not match the convolution geometry")
+    dx = torch.empty((B, H, W, C), device=grad_out.device, dtype=grad_out.dtype)
+    g = _geom((B, H, W, C), k, stride, padding, dilation)
+    with torch.cuda.device(grad_out.device):
+        rc = _lib.lib().pdw_dwconv_bwd_input(_ptr(grad_out), _ptr(weight), _ptr(dx), ctypes.byref(g),
+                                             _dtype_code(grad_out), _ptr(status_word(grad_out.device)),
+                                             _stream(grad_out))
+    _lib.check(rc, "pdw_dwconv_bwd_input")
+    return dx
+
+
+def dwconv_backward_weight(x, grad_out, kernel_size, stride=1, padding=0, dilation=1, with_bias=False,
+                           out_dtype=None):
+    """(dW[KH,KW,C], dbias[C] or None); sums are carried in fp32 and cast once at the end.
+
+    ``out_dtype=torch.float32`` returns the fp32 sums uncast (e.g. to feed an all-reduce)."""
+    _require_cuda(x, grad_out)
+    _check_nhwc(x, "input")
+    _check_nhwc(grad_out, "grad_output")
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    k = _pair(kernel_size)
+    if x.dtype != grad_out.dtype:
+        raise RuntimeError("input and grad_output must share one dtype")
+    x, grad_out = x.contiguous(), grad_out.contiguous()
+    B, H, W, C = x.shape
+    if tuple(grad_out.shape) != (B,) + conv_out_hw(H, W, k, stride, padding, dilation) + (C,):
+        raise RuntimeError("grad_output extent does not match the convolution geometry")
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise RuntimeError("out_dtype must be the input dtype or float32")
+    out_fp32 = int(out_dtype == torch.float32 and x.dtype != torch.float32)
+    dw = torch.empty((k[0], k[1], C), device=x.device, dtype=out_dtype)
+    dbias = torch.empty((C,), device=x.device, dtype=out_dtype) if with_bias else None
+    g = _geom(x.shape, k, stride, padding, dilation)
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        need = L.pdw_dwconv_bwd_weight_workspace(ctypes.byref(g), _dtype_code(x))
+        ws = torch.empty((max(need, 16),), device=x.device, dtype=torch.uint8)
+        rc = L.pdw_dwconv_bwd_weight(_ptr(x), _ptr(grad_out), _ptr(dw), _ptr(dbias), ctypes.byref(g), _dtype_code(x),
+                                     out_fp32, _ptr(ws), need, _ptr(status_word(x.device)), _stream(x))
+    _lib.check(rc, "pdw_dwconv_bwd_weight")
+    return dw, dbias
+
+
+def _resample(fn_name, src, out_shape, H, W, OH, OW):
+    _require_cuda(src)
+    src = src.contiguous()
+    dst = torch.empty(out_shape, device=src.device, dtype=src.dtype)
+    B, C = src.shape[0], src.shape[3]
+    with torch.cuda.device(src.device):
+        rc = getattr(_lib.lib(), fn_name)(_ptr(src), _ptr(dst), B, H, W, C, OH, OW, _dtype_code(src), _stream(src))
+    _lib.check(rc, fn_name)
+    return dst
+
+
+def pool_forward(x, output_size):
+    _check_nhwc(x, "input")
+    OH, OW = _pair(output_size)
+    B, H, W, C = x.shape
+    return _resample("pdw_pool_fwd", x, (B, OH, OW, C), H, W, OH, OW)
+
+
+def pool_backward(grad_out, input_hw):
+    _check_nhwc(grad_out, "grad_output")
+    B, OH, OW, C = grad_out.shape
+    H, W = input_hw
+    return _resample("pdw_pool_bwd", grad_out, (B, H, W, C), H, W, OH, OW)
+
+
+def upsample_forward(x, output_size):
+    _check_nhwc(x, "input")
+    OH, OW = _pair(output_size)
+    B, H, W, C = x.shape
+    return _resample("pdw_upsample_fwd", x, (B, OH, OW, C), H, W, OH, OW)
+
+
+def upsample_backward(grad_out, input_hw):
+    _check_nhwc(grad_out, "grad_output")
+    B, OH, OW, C = grad_out.shape
+    H, W = input_hw
+    return _resample("pdw_upsample_bwd", grad_out, (B, H, W, C), H, W, OH, OW)
+
+
+def gate_forward(conv_out, inv_scale):
+    """y[..., :C/2] = x1 * (x2 * inv_scale) for conv_out = cat(x1, x2) on the last axis."""
+    _require_cuda(conv_out)
+    conv_out = conv_out.contiguous()
+    C = conv_out.shape[-1]
+    if C % 2:
+        raise RuntimeError("the gate needs an even channel count")
+    pixels = conv_out.numel() // C
+    y = torch.empty(conv_out.shape[:-1] + (C // 2,), device=conv_out.device, dtype=conv_out.dtype)
+    with torch.cuda.device(conv_out.device):
+        rc = _lib.lib().pdw_gate_fwd(_ptr(conv_out), _ptr(y), pixels, C, float(inv_scale), _dtype_code(conv_out),
+                                     _stream(conv_out))
+    _lib.check(rc, "pdw_gate_fwd")
+    return y
+
+
+def gate_backward(conv_out, grad_y, inv_scale):
+    _require_cuda(conv_out, grad_y)
+    conv_out, grad_y = conv_out.contiguous(), grad_y.contiguous()
+    C = conv_out.shape[-1]
+    pixels = conv_out.numel() // C
+    ga = torch.empty_like(conv_out)
+    with torch.cuda.device(conv_out.device):
+        rc = _lib.lib().pdw_gate_bwd(_ptr(conv_out), _ptr(grad_y), _ptr(ga), pixels, C, float(inv_scale),
+                                     _dtype_code(conv_out), _stream(conv_out))
+    _lib.check(rc, "pdw_gate_bwd")
+    return ga
+
+
+class DepthwiseConv2DFunction(torch.autograd.Function):
+    """Drop-in for the reference Function (pyramid_dwconv/dwconv_triton.py:299-387).
+
+    ``apply(input, weight, stride, padding, dilation, dtype[, bias])``: input [B,H,W,C], weight
+    [KH,KW,C]; the output has dtype ``dtype`` (the reference allocates it so, :314-315).  backward
+    returns ``(dX, dW, None, None, None, None, dbias)``; dX has the input's dtype and dW the
+    weight's, as in the reference (:346-347), but dW is summed in fp32 without atomics and every
+    stride/padding/dilation has a correct backward.
+    """
+
+    @staticmethod
+    def forward(ctx, input, weight, stride, padding, dilation, dtype, bias=None):
+        stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+        dtype = weight.dtype if dtype is None else dtype
+        compute = torch.promote_types(input.dtype, weight.dtype)
+        x = input if input.dtype == compute else input.to(compute)
+        w = weight if weight.dtype == compute else weight.to(compute)
+        b = None if bias is None else bias.to(compute)
+        y = dwconv_forward(x, w, b, stride, padding, dilation)
+        ctx.save_for_backward(input, weight)
+        ctx.geometry = (stride, padding, dilation)
+        ctx.compute = compute
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = None if bias is None else bias.dtype
+        return y if y.dtype == dtype else y.to(dtype)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight = ctx.saved_tensors
+        stride, padding, dilation = ctx.geometry
+        compute = ctx.compute
+        g = grad_output if grad_output.dtype == compute else grad_output.to(compute)
+        grad_input = grad_weight = grad_bias = None
+        need_w = ctx.needs_input_grad[1]
+        need_b = ctx.has_bias and ctx.needs_input_grad[6]
+        # Parameter gradients first: whoever reduces them across ranks can start while dX runs.
+        if need_w or need_b:
+            x = input if input.dtype == compute else input.to(compute)
+            dw, db = dwconv_backward_weight(x, g, weight.shape[:2], stride, padding, dilation, with_bias=need_b)
+            if need_w:
+                grad_weight = dw if dw.dtype == weight.dtype else dw.to(weight.dtype)
+            if need_b:
+                grad_bias = db if db.dtype == ctx.bias_dtype else db.to(ctx.bias_dtype)
+        if ctx.needs_input_grad[0]:
+            w = weight if weight.dtype == compute else weight.to(compute)
+            dx = dwconv_backward_input(g, w, input.shape[1:3], stride, padding, dilation)
+            grad_input = dx if dx.dtype == input.dtype else dx.to(input.dtype)
+        return grad_input, grad_weight, None, None, None, None, grad_bias
+
+
+class AdaptiveAvgPool2dFunction(torch.autograd.Function):
+    """Drop-in for pyramid_dwconv/avgpool_triton.py:205-257: ``apply(input[B,H,W,C], (OH,OW))``."""
+
+    @staticmethod
+    def forward(ctx, input, output_size):
+        ctx.input_hw = (input.shape[1], input.shape[2])
+        return pool_forward(input, output_size)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return pool_backward(grad_output, ctx.input_hw), None
+
+
+class BilinearInterp2dFunction(torch.autograd.Function):
+    """Bilinear resize (align_corners=False) of [B,h,w,C] to (H,W) with a backward pass; the
+    reference's up_triton.py:127-162 is forward only."""
+
+    @staticmethod
+    def forward(ctx, input, output_size):
+        ctx.input_hw = (input.shape[1], input.shape[2])
+        return upsample_forward(input, output_size)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return upsample_backward(grad_output, ctx.input_hw), None
+
+
+class GateFunction(torch.autograd.Function):
+    """x1 * (x2 / scale) over the two channel halves (pyramid_dwconv/conv_block.py:18-19)."""
+
+    @staticmethod
+    def forward(ctx, conv_out, inv_scale):
+        ctx.save_for_backward(conv_out)
+        ctx.inv_scale = inv_scale
+        return gate_forward(conv_out, inv_scale)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        (conv_out,) = ctx.saved_tensors
+        return gate_backward(conv_out, grad_y, ctx.inv_scale), None

@@ -1,0 +1,164 @@
+"""Generate the golden fixtures in this folder by running the UNMODIFIED reference.
+
+The reference (IrisRainbowNeko/PyramidConvBlock, package ``pyramid_dwconv``) is pure
+Python + Triton.  Its kernels run on a CPU-only machine under ``TRITON_INTERPRET=1``
+once every ``@triton.autotune`` list is trimmed to a single config (the autotuner
+otherwise tries to benchmark on a GPU).  No reference file is modified; the trimming
+happens on the imported objects.
+
+Usage (only where the reference checkout exists)::
+
+    python tests/golden/make_golden.py [--reference /path/to/PyramidConvBlock]
+
+Outputs (all ``.npz``, float32 unless noted):
+
+* ``convblock_cfg1.npz``   - ConvBlock(dim=64, kernel_size=9).to(float32) forward and
+  backward on x[2,32,32,64] (seed 0), upstream grad (seed 1), default init under
+  ``torch.manual_seed(0)``: the seeded parameters, y, dX and every parameter gradient.
+* ``dwconv_small.npz``     - DepthwiseConv2DFunction forward/backward on small shapes
+  (pyramid_dwconv/dwconv_triton.py:299-387), several kernel sizes.
+* ``pool_small.npz``       - AdaptiveAvgPool2dFunction forward/backward
+  (pyramid_dwconv/avgpool_triton.py:205-257) on sizes where the reference's fp16 window
+  arithmetic is exact.
+* ``upsample_small.npz``   - OptimizedBilinearInterp2d forward
+  (pyramid_dwconv/up_triton.py:127-162).
+
+Inputs are never stored: every test re-draws them from the seeds recorded here with
+``torch.Generator().manual_seed(seed)`` on the CPU, exactly as this script does.
+"""
+import argparse
+import os
+import sys
+
+os.environ["TRITON_INTERPRET"] = "1"
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def randn(shape, seed, gen=None):
+    g = gen if gen is not None else torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g, dtype=torch.float32)
+
+
+def import_reference(path):
+    sys.path.insert(0, path)
+    import pyramid_dwconv  # noqa: F401
+    from pyramid_dwconv import avgpool_triton, conv_block, dwconv_triton, up_triton
+
+    for mod in (dwconv_triton, avgpool_triton, up_triton):
+        for name in dir(mod):
+            obj = getattr(mod, name)
+            if hasattr(obj, "configs") and isinstance(getattr(obj, "configs"), list):
+                obj.configs = obj.configs[1:2]  # (16,16,64) for every kernel
+    return dwconv_triton, avgpool_triton, up_triton, conv_block
+
+
+def gen_convblock(conv_block):
+    torch.manual_seed(0)
+    m = conv_block.ConvBlock(64, kernel_size=9).to(torch.float32)
+    x = randn((2, 32, 32, 64), 0).requires_grad_(True)
+    gout = randn((2, 32, 32, 64), 1)
+    y = m(x)
+    y.backward(gout)
+    out = {"y": y.detach().numpy(), "dx": x.grad.numpy()}
+    for k, v in m.state_dict().items():
+        out["param." + k] = v.numpy()
+    for k, p in m.named_parameters():
+        out["grad." + k] = p.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "convblock_cfg1.npz"), **out)
+    print("convblock_cfg1: y", tuple(y.shape), "params", len(m.state_dict()))
+
+
+DWCONV_CASES = [
+    # name, B, H, W, C, k, seed
+    ("k3", 2, 9, 11, 16, 3, 10),
+    ("k9", 1, 20, 18, 16, 9, 11),
+    ("k13", 1, 16, 22, 8, 13, 12),
+    ("k17", 1, 19, 17, 8, 17, 13),
+]
+
+
+def gen_dwconv(dwconv_triton):
+    out = {}
+    F = dwconv_triton.DepthwiseConv2DFunction
+    for name, B, H, W, C, k, seed in DWCONV_CASES:
+        g = torch.Generator().manual_seed(seed)
+        x = randn((B, H, W, C), None, g).requires_grad_(True)
+        w = (randn((k, k, C), None, g) / k).requires_grad_(True)
+        gout = randn((B, H, W, C), None, g)
+        p = k // 2
+        y = F.apply(x, w, (1, 1), (p, p), (1, 1), torch.float32)
+        y.backward(gout)
+        out[name + ".y"] = y.detach().numpy()
+        out[name + ".dx"] = x.grad.numpy()
+        out[name + ".dw"] = w.grad.numpy()
+        out[name + ".meta"] = np.array([B, H, W, C, k, seed])
+        print("dwconv", name, "ok")
+    # forward only with stride 2 / dilation 2 / no padding (the reference's forward is
+    # general; its backward is only right for stride 1 + same padding).
+    g = torch.Generator().manual_seed(20)
+    x = randn((1, 17, 15, 8), None, g)
+    w = randn((5, 5, 8), None, g) / 5
+    with torch.no_grad():
+        out["general.s2p1.y"] = F.apply(x, w, (2, 2), (1, 1), (1, 1), torch.float32).numpy()
+        out["general.d2p4.y"] = F.apply(x, w, (1, 1), (4, 4), (2, 2), torch.float32).numpy()
+        out["general.p0.y"] = F.apply(x, w, (1, 1), (0, 0), (1, 1), torch.float32).numpy()
+    out["general.meta"] = np.array([1, 17, 15, 8, 5, 20])
+    # one fp16 forward (inputs rounded to fp16, output fp16)
+    g = torch.Generator().manual_seed(21)
+    x = randn((1, 16, 16, 16), None, g).half()
+    w = (randn((9, 9, 16), None, g) / 9).half()
+    with torch.no_grad():
+        out["half.k9.y"] = F.apply(x, w, (1, 1), (4, 4), (1, 1), torch.float16).float().numpy()
+    out["half.meta"] = np.array([1, 16, 16, 16, 9, 21])
+    np.savez_compressed(os.path.join(HERE, "dwconv_small.npz"), **out)
+
+
+POOL_CASES = [("16to8", 2, 16, 16, 16, 8, 8, 30), ("16to4", 1, 16, 16, 8, 4, 4, 31), ("12x8to6x2", 1, 12, 8, 8, 6, 2, 32)]
+
+
+def gen_pool(avgpool_triton):
+    out = {}
+    F = avgpool_triton.AdaptiveAvgPool2dFunction
+    for name, B, H, W, C, oh, ow, seed in POOL_CASES:
+        g = torch.Generator().manual_seed(seed)
+        x = randn((B, H, W, C), None, g).requires_grad_(True)
+        gout = randn((B, oh, ow, C), None, g)
+        y = F.apply(x, (oh, ow))
+        y.backward(gout)
+        out[name + ".y"] = y.detach().numpy()
+        out[name + ".dx"] = x.grad.numpy()
+        out[name + ".meta"] = np.array([B, H, W, C, oh, ow, seed])
+        print("pool", name, "ok")
+    np.savez_compressed(os.path.join(HERE, "pool_small.npz"), **out)
+
+
+UP_CASES = [("8to16", 2, 8, 8, 16, 16, 16, 40), ("6x5to15x11", 1, 6, 5, 8, 15, 11, 41), ("4to16", 1, 4, 4, 8, 16, 16, 42)]
+
+
+def gen_up(up_triton):
+    out = {}
+    for name, B, h, w, C, H, W, seed in UP_CASES:
+        g = torch.Generator().manual_seed(seed)
+        x = randn((B, h, w, C), None, g)
+        m = up_triton.OptimizedBilinearInterp2d((H, W))
+        with torch.no_grad():
+            y = m(x)
+        out[name + ".y"] = y.numpy()
+        out[name + ".meta"] = np.array([B, h, w, C, H, W, seed])
+        print("upsample", name, "ok")
+    np.savez_compressed(os.path.join(HERE, "upsample_small.npz"), **out)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    dw, ap_, up, cb = import_reference(args.reference)
+    gen_dwconv(dw)
+    gen_pool(ap_)
+    gen_up(up)
+    gen_convblock(cb)
