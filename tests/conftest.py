@@ -1,0 +1,59 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+def golden(name):
+    return np.load(os.path.join(GOLDEN, name))
+
+
+def draw(shapes, seed, scale=None):
+    """Tensors drawn in order from ONE CPU generator, as tests/golden/make_golden.py does."""
+    g = torch.Generator().manual_seed(int(seed))
+    out = [torch.randn(tuple(int(v) for v in s), generator=g, dtype=torch.float32) for s in shapes]
+    return out
+
+
+def assert_close_fp32(actual, expected, what="", rtol=1e-5, atol_rel=1e-5):
+    """fp32 bar: |a - e| <= rtol*|e| + atol_rel*max|e|.
+
+    A pure relative test is meaningless for elements that cancel to ~0; the absolute term is tied
+    to the tensor's own magnitude (1e-5 of its largest element)."""
+    a = np.asarray(actual, dtype=np.float64)
+    e = np.asarray(expected, dtype=np.float64)
+    assert a.shape == e.shape, "%s: shape %s vs %s" % (what, a.shape, e.shape)
+    atol = atol_rel * max(float(np.abs(e).max()), 1e-30)
+    err = np.abs(a - e) - (rtol * np.abs(e) + atol)
+    assert err.max() <= 0, "%s: max violation %.3e (max abs err %.3e, max |ref| %.3e)" % (
+        what, err.max(), np.abs(a - e).max(), np.abs(e).max())
+
+
+def assert_close_16bit(actual, expected, what="", rtol=2e-2, atol=2e-3):
+    """fp16/bf16 bar versus an fp32/fp64 reference: rtol 2e-2, atol 2e-3."""
+    a = np.asarray(actual, dtype=np.float64)
+    e = np.asarray(expected, dtype=np.float64)
+    assert a.shape == e.shape, "%s: shape %s vs %s" % (what, a.shape, e.shape)
+    err = np.abs(a - e) - (rtol * np.abs(e) + atol)
+    assert err.max() <= 0, "%s: max violation %.3e (max abs err %.3e, max |ref| %.3e)" % (
+        what, err.max(), np.abs(a - e).max(), np.abs(e).max())

@@ -1,0 +1,234 @@
+"""GPU parity tests: every C-ABI kernel against the CPU oracle on the same seeded inputs, plus the
+golden outputs of the unmodified reference.  fp32 bar: rtol 1e-5 (+1e-5 of the tensor's max as
+absolute floor); fp16/bf16 bar: rtol 2e-2 / atol 2e-3 versus the oracle run on the rounded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close_16bit, assert_close_fp32, draw, golden
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+from pyramidconvblock_b200 import _lib, ops  # noqa: E402
+
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def close(dtype):
+    return assert_close_fp32 if dtype == torch.float32 else assert_close_16bit
+
+
+def to_dev(t, dtype):
+    return t.to(dtype).cuda()
+
+
+def rounded(t, dtype):
+    """What the kernel actually sees: the fp32 draw rounded to `dtype`."""
+    return t.to(dtype).float()
+
+
+@pytest.fixture(autouse=True)
+def _reset_tuning_and_check_status():
+    L = _lib.lib()
+    L.pdw_set_tuning(0, 0)
+    L.pdw_set_tuning(1, 16)
+    L.pdw_set_tuning(2, 0)
+    yield
+    L.pdw_set_tuning(0, 0)
+    L.pdw_set_tuning(1, 16)
+    L.pdw_set_tuning(2, 0)
+    ops.check_device_status()
+
+
+def run_conv_case(B, H, W, C, k, dtype, seed, stride=1, padding=None, dilation=1, bias=True):
+    k = (k, k) if isinstance(k, int) else k
+    padding = (k[0] // 2, k[1] // 2) if padding is None else padding
+    x, w, b = draw([(B, H, W, C), k + (C,), (C,)], seed)
+    w = w / float(np.sqrt(k[0] * k[1]))
+    b = b * 0.1
+    xr, wr, br = rounded(x, dtype), rounded(w, dtype), rounded(b, dtype)
+    y_ref = oracle.c_dwconv_fwd(xr, wr, br if bias else None, stride, padding, dilation)
+    (go,) = draw([y_ref.shape], seed + 1000)
+    gr = rounded(go, dtype)
+    dx_ref = oracle.c_dwconv_bwd_input(gr, wr, (H, W), stride, padding, dilation)
+    dw_ref, db_ref = oracle.c_dwconv_bwd_weight(xr, gr, k, stride, padding, dilation)
+
+    xd, wd, bd, gd = to_dev(x, dtype), to_dev(w, dtype), to_dev(b, dtype), to_dev(go, dtype)
+    y = ops.dwconv_forward(xd, wd, bd if bias else None, stride, padding, dilation)
+    dx = ops.dwconv_backward_input(gd, wd, (H, W), stride, padding, dilation)
+    dw, db = ops.dwconv_backward_weight(xd, gd, k, stride, padding, dilation, with_bias=True)
+    torch.cuda.synchronize()
+    chk = close(dtype)
+    chk(y.float().cpu().numpy(), y_ref, "y")
+    chk(dx.float().cpu().numpy(), dx_ref, "dx")
+    if dtype == torch.float32:
+        chk(dw.cpu().numpy(), dw_ref, "dw")
+        chk(db.cpu().numpy(), db_ref, "dbias")
+    else:
+        # sums are carried in fp32; the 16-bit cast of the result is the only 16-bit rounding
+        dw32, db32 = ops.dwconv_backward_weight(xd, gd, k, stride, padding, dilation, with_bias=True,
+                                                out_dtype=torch.float32)
+        assert_close_fp32(dw32.cpu().numpy(), dw_ref, "dw fp32 sums", rtol=1e-4, atol_rel=1e-5)
+        assert_close_fp32(db32.cpu().numpy(), db_ref, "dbias fp32 sums", rtol=1e-4, atol_rel=1e-5)
+        assert_close_16bit(dw.float().cpu().numpy(), dw_ref, "dw", atol=2e-3 + 4e-3 * np.abs(dw_ref).max())
+        assert_close_16bit(db.float().cpu().numpy(), db_ref, "dbias", atol=2e-3 + 4e-3 * np.abs(db_ref).max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("k", [3, 5, 7, 9, 11, 13, 15, 17])
+def test_dwconv_tiled_all_widths(k, dtype):
+    run_conv_case(2, 21, 19, 16, k, dtype, seed=100 + k)
+
+
+@pytest.mark.parametrize("math,ct", [(0, 16), (1, 16), (0, 32), (1, 32)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k", [9, 13, 17])
+def test_dwconv_inner_loop_variants_agree(k, dtype, math, ct):
+    L = _lib.lib()
+    L.pdw_set_tuning(0, math)
+    L.pdw_set_tuning(1, ct)
+    run_conv_case(1, 40, 37, 48, k, dtype, seed=200 + k)
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 1, 1, 8),      # single pixel
+    (3, 5, 70, 8),     # wide and flat, more than one column tile
+    (1, 67, 9, 24),    # tall, channels not a multiple of the tile
+    (2, 33, 33, 40),   # just over a tile in both directions
+    (1, 128, 128, 16), # many tiles
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_dwconv_ragged_shapes(shape, dtype):
+    run_conv_case(*shape, 9, dtype, seed=300 + shape[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dwconv_padding_other_than_same(dtype):
+    run_conv_case(2, 20, 23, 16, 7, dtype, seed=400, padding=(0, 0))
+    run_conv_case(2, 20, 23, 16, 7, dtype, seed=401, padding=(1, 5))
+    run_conv_case(1, 12, 12, 8, 5, dtype, seed=402, padding=(4, 4))   # output larger than input
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("geom", [
+    dict(k=(5, 5), stride=2, padding=1, dilation=1),
+    dict(k=(5, 5), stride=1, padding=4, dilation=2),
+    dict(k=(3, 7), stride=(2, 1), padding=(1, 3), dilation=1),     # non-square kernel
+    dict(k=(4, 4), stride=1, padding=2, dilation=1),               # even width: untiled kernels
+    dict(k=(9, 9), stride=1, padding=4, dilation=1, C=6),          # channel count TMA cannot address
+])
+def test_dwconv_general_geometry(geom, dtype):
+    C = geom.get("C", 8)
+    run_conv_case(2, 17, 15, C, geom["k"], dtype, seed=500, stride=geom["stride"], padding=geom["padding"],
+                  dilation=geom["dilation"])
+
+
+def test_dwconv_untiled_kernels_agree_with_tiled():
+    _lib.lib().pdw_set_tuning(2, 1)
+    run_conv_case(2, 21, 19, 16, 9, torch.float16, seed=600)
+    run_conv_case(1, 21, 19, 16, 13, torch.float32, seed=601)
+
+
+def test_dwconv_without_bias_and_reference_golden():
+    g = golden("dwconv_small.npz")
+    for name in ["k3", "k9", "k13", "k17"]:
+        B, H, W, C, k, seed = [int(v) for v in g[name + ".meta"]]
+        x, w, go = draw([(B, H, W, C), (k, k, C), (B, H, W, C)], seed)
+        w = w / k
+        p = k // 2
+        xd, wd, gd = x.cuda(), w.cuda(), go.cuda()
+        assert_close_fp32(ops.dwconv_forward(xd, wd, None, 1, p, 1).cpu().numpy(), g[name + ".y"], name + " y")
+        assert_close_fp32(ops.dwconv_backward_input(gd, wd, (H, W), 1, p, 1).cpu().numpy(), g[name + ".dx"], name + " dx")
+        dw, db = ops.dwconv_backward_weight(xd, gd, k, 1, p, 1)
+        assert db is None
+        assert_close_fp32(dw.cpu().numpy(), g[name + ".dw"], name + " dw")
+    B, H, W, C, k, seed = [int(v) for v in g["general.meta"]]
+    x, w = draw([(B, H, W, C), (k, k, C)], seed)
+    xd, wd = x.cuda(), (w / k).cuda()
+    assert_close_fp32(ops.dwconv_forward(xd, wd, None, 2, 1, 1).cpu().numpy(), g["general.s2p1.y"])
+    assert_close_fp32(ops.dwconv_forward(xd, wd, None, 1, 4, 2).cpu().numpy(), g["general.d2p4.y"])
+    assert_close_fp32(ops.dwconv_forward(xd, wd, None, 1, 0, 1).cpu().numpy(), g["general.p0.y"])
+
+
+def test_dwconv_weight_gradient_is_bitwise_reproducible():
+    x, go = draw([(4, 64, 64, 32), (4, 64, 64, 32)], 700)
+    xd, gd = x.half().cuda(), go.half().cuda()
+    a, ab = ops.dwconv_backward_weight(xd, gd, 13, 1, 6, 1, with_bias=True, out_dtype=torch.float32)
+    b, bb = ops.dwconv_backward_weight(xd, gd, 13, 1, 6, 1, with_bias=True, out_dtype=torch.float32)
+    assert torch.equal(a, b) and torch.equal(ab, bb)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", [((16, 16), (8, 8)), ((15, 9), (4, 7)), ((7, 7), (7, 7)), ((5, 6), (9, 8)),
+                                   ((32, 32), (4, 4)), ((9, 9), (1, 1))])
+@pytest.mark.parametrize("C", [8, 6])
+def test_pool_forward_backward(sizes, dtype, C):
+    (H, W), (OH, OW) = sizes
+    x, go = draw([(2, H, W, C), (2, OH, OW, C)], 800 + H)
+    chk = close(dtype)
+    y = ops.pool_forward(to_dev(x, dtype), (OH, OW))
+    dx = ops.pool_backward(to_dev(go, dtype), (H, W))
+    chk(y.float().cpu().numpy(), oracle.c_pool_fwd(rounded(x, dtype).numpy(), (OH, OW)), "y")
+    chk(dx.float().cpu().numpy(), oracle.c_pool_bwd(rounded(go, dtype).numpy(), (H, W)), "dx")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", [((8, 8), (16, 16)), ((6, 5), (15, 11)), ((4, 4), (16, 16)), ((7, 7), (7, 7)),
+                                   ((16, 12), (5, 7)), ((1, 1), (4, 4)), ((3, 2), (24, 32))])
+@pytest.mark.parametrize("C", [8, 6])
+def test_upsample_forward_backward(sizes, dtype, C):
+    (h, w), (H, W) = sizes
+    x, go = draw([(2, h, w, C), (2, H, W, C)], 900 + h)
+    chk = close(dtype)
+    y = ops.upsample_forward(to_dev(x, dtype), (H, W))
+    dx = ops.upsample_backward(to_dev(go, dtype), (h, w))
+    chk(y.float().cpu().numpy(), oracle.c_upsample_fwd(rounded(x, dtype).numpy(), (H, W)), "y")
+    chk(dx.float().cpu().numpy(), oracle.c_upsample_bwd(rounded(go, dtype).numpy(), (h, w)), "dx")
+
+
+def test_pool_and_upsample_reference_golden():
+    g = golden("pool_small.npz")
+    for name in ["16to8", "16to4", "12x8to6x2"]:
+        B, H, W, C, oh, ow, seed = [int(v) for v in g[name + ".meta"]]
+        x, go = draw([(B, H, W, C), (B, oh, ow, C)], seed)
+        assert_close_fp32(ops.pool_forward(x.cuda(), (oh, ow)).cpu().numpy(), g[name + ".y"])
+        assert_close_fp32(ops.pool_backward(go.cuda(), (H, W)).cpu().numpy(), g[name + ".dx"])
+    g = golden("upsample_small.npz")
+    for name in ["8to16", "6x5to15x11", "4to16"]:
+        B, h, w, C, H, W, seed = [int(v) for v in g[name + ".meta"]]
+        (x,) = draw([(B, h, w, C)], seed)
+        assert_close_fp32(ops.upsample_forward(x.cuda(), (H, W)).cpu().numpy(), g[name + ".y"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("C", [32, 12])
+def test_gate_forward_backward(dtype, C):
+    a, gy = draw([(2, 5, 7, C), (2, 5, 7, C // 2)], 1000)
+    inv = 1.0 / (C / 2) ** -0.5
+    ar, gr = rounded(a, dtype), rounded(gy, dtype)
+    x1, x2 = ar.double().chunk(2, dim=-1)
+    y_ref = x1 * (x2 * inv)
+    ga_ref = torch.cat([gr.double() * x2 * inv, gr.double() * x1 * inv], dim=-1)
+    y = ops.gate_forward(to_dev(a, dtype), inv)
+    ga = ops.gate_backward(to_dev(a, dtype), to_dev(gy, dtype), inv)
+    chk = close(dtype)
+    chk(y.float().cpu().numpy(), y_ref.numpy(), "y")
+    chk(ga.float().cpu().numpy(), ga_ref.numpy(), "ga")
+
+
+def test_known_answers_on_gpu():
+    (x,) = draw([(1, 20, 33, 16)], 1100)
+    w = torch.zeros(9, 9, 16)
+    w[4, 4, :] = 1
+    y = ops.dwconv_forward(x.cuda(), w.cuda(), None, 1, 4, 1)
+    assert torch.equal(y.cpu(), x)                       # centred delta filter = identity, bit exact
+    w = torch.zeros(9, 9, 16)
+    w[0, 8, :] = 1                                       # a corner tap = pure shift with zero fill
+    y = ops.dwconv_forward(x.cuda(), w.cuda(), None, 1, 4, 1).cpu()
+    expect = torch.zeros_like(x)
+    expect[:, 4:, :-4, :] = x[:, :-4, 4:, :]
+    assert torch.equal(y, expect)
+    const = torch.full((1, 9, 7, 8), 3.25).cuda()
+    assert torch.allclose(ops.pool_forward(const, (4, 3)), torch.tensor(3.25).cuda())
+    assert torch.allclose(ops.upsample_forward(const, (18, 15)), torch.tensor(3.25).cuda())

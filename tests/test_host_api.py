@@ -1,0 +1,104 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports every symbol the header
+declares, argument validation returns the documented status codes before any launch, the modules
+reproduce the reference's seeded parameters and refuse CPU tensors."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, golden
+
+from pyramidconvblock_b200 import _lib
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "pdw_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(pdw_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert set(_lib.EXPORTED_SYMBOLS) <= declared
+    L = _lib.lib()
+    for name in sorted(declared):
+        assert hasattr(L, name), "libpdw_b200.so does not export %s" % name
+
+
+def test_version_status_strings_and_out_size():
+    L = _lib.lib()
+    assert L.pdw_version() >= 100
+    assert L.pdw_status_string(0) == b"ok"
+    for code in range(1, 10):
+        assert len(L.pdw_status_string(code)) > 3
+    # formula of pyramid_dwconv/dwconv_triton.py:311-312
+    for (i, k, s, p, d) in [(32, 9, 1, 4, 1), (17, 5, 2, 1, 1), (15, 5, 1, 4, 2), (7, 7, 1, 0, 1), (3, 7, 1, 0, 1)]:
+        expect = max((i + 2 * p - d * (k - 1) - 1), -1)
+        expect = expect // s + 1 if expect >= 0 else 0
+        assert L.pdw_conv_out_size(i, k, s, p, d) == expect
+
+
+def test_argument_validation_without_launch():
+    L = _lib.lib()
+    g = _lib.ConvGeom(1, 8, 8, 8, 3, 3, 1, 1, 1, 1, 1, 1)
+    fake = ctypes.c_void_p(256)   # never dereferenced: validation happens first
+    assert L.pdw_dwconv_fwd(None, fake, None, fake, ctypes.byref(g), 1, None, None) == 1
+    assert L.pdw_dwconv_fwd(fake, fake, None, fake, None, 1, None, None) == 1
+    assert L.pdw_dwconv_fwd(fake, fake, None, fake, ctypes.byref(g), 7, None, None) == 2
+    bad = _lib.ConvGeom(1, 8, 8, 0, 3, 3, 1, 1, 1, 1, 1, 1)
+    assert L.pdw_dwconv_fwd(fake, fake, None, fake, ctypes.byref(bad), 1, None, None) == 3
+    empty = _lib.ConvGeom(1, 4, 4, 8, 9, 9, 1, 1, 0, 0, 1, 1)   # kernel larger than the padded image
+    assert L.pdw_dwconv_bwd_input(fake, fake, fake, ctypes.byref(empty), 0, None, None) == 3
+    odd = ctypes.c_void_p(257)
+    assert L.pdw_dwconv_fwd(odd, fake, None, fake, ctypes.byref(g), 1, None, None) == 6
+    assert L.pdw_pool_fwd(None, fake, 1, 8, 8, 8, 4, 4, 1, None) == 1
+    assert L.pdw_pool_fwd(fake, fake, 1, 8, 8, 8, 0, 4, 1, None) == 3
+    assert L.pdw_upsample_bwd(fake, fake, 1, 8, 8, 8, 16, 16, 9, None) == 2
+    assert L.pdw_gate_fwd(fake, fake, 10, 7, 1.0, 1, None) == 3
+    assert L.pdw_set_tuning(9, 0) == -1
+    assert L.pdw_set_tuning(1, 24) == -1
+
+
+def test_seeded_parameters_match_reference():
+    """Same creation order, shapes and dtypes as the reference => same RNG stream => same weights."""
+    from pyramid_dwconv import ConvBlock
+    g = golden("convblock_cfg1.npz")
+    torch.manual_seed(0)
+    m = ConvBlock(64, kernel_size=9)
+    assert m.gates[0].conv_spatial.weight.dtype == torch.float16   # created in fp16 whatever dtype says
+    m = m.to(torch.float32)
+    keys = [k[len("param."):] for k in g.files if k.startswith("param.")]
+    assert list(m.state_dict().keys()) == keys
+    for k, v in m.state_dict().items():
+        assert np.array_equal(v.numpy(), g["param." + k]), k
+
+
+def test_import_surface_and_cpu_refusal():
+    import pyramid_dwconv
+    from pyramid_dwconv import ConvBlock, DepthwiseConv2DFunction, OptimizedDepthwiseConv2d  # noqa: F401
+    from pyramid_dwconv.avgpool_triton import OptimizedAdaptiveAvgPool2d
+    from pyramid_dwconv.conv_block import SimpleGate  # noqa: F401
+    from pyramid_dwconv.dwconv_triton import OptimizedDepthwiseConv2d as again
+    from pyramid_dwconv.up_triton import OptimizedBilinearInterp2d
+    assert again is OptimizedDepthwiseConv2d
+    conv = OptimizedDepthwiseConv2d(8, 3, padding=1)
+    assert conv.weight.shape == (3, 3, 8) and conv.kernel_size == (3, 3) and conv.padding == (1, 1)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        conv(torch.randn(1, 4, 4, 8).half())
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        OptimizedAdaptiveAvgPool2d(2)(torch.randn(1, 4, 4, 8))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        OptimizedBilinearInterp2d(8)(torch.randn(1, 4, 4, 8))
+    with pytest.raises(AssertionError):
+        conv(torch.randn(1, 4, 4, 6).half())
+    with pytest.raises(NotImplementedError):
+        OptimizedBilinearInterp2d(8, align_corners=True)
+    assert not hasattr(pyramid_dwconv, "triton")
+
+
+def test_product_package_does_not_import_the_oracle():
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r); import pyramid_dwconv, pyramidconvblock_b200; "
+            "assert not any(m == 'oracle' or m.startswith('oracle.') for m in sys.modules), 'oracle imported'" % ROOT)
+    subprocess.run([sys.executable, "-c", code], check=True)
