@@ -62,11 +62,6 @@ def _declare(lib):
     lib.pdw_gate_bwd.argtypes = [vp, vp, vp, i64, i32, f32, i32, vp]
     lib.pdw_set_tuning.restype = i32
     lib.pdw_set_tuning.argtypes = [i32, i32]
-    if hasattr(lib, "pdw_dwconv_bwd_weight_static"):
-        lib.pdw_dwconv_bwd_weight_static.restype = i32
-        lib.pdw_dwconv_bwd_weight_static.argtypes = [vp, vp, vp, vp, geom, i32, i32, vp, vp]
-        lib.pdw_static_scratch_bytes.restype = sz
-        lib.pdw_static_scratch_bytes.argtypes = []
 
 
 def lib():

@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(HERE, "libpdw_b200.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 FILTER_WIDTHS = (3, 5, 7, 9, 11, 13, 15, 17)
-PLAIN_SOURCES = ("dwconv.cu", "resample.cu", "static_scratch.cu")
+PLAIN_SOURCES = ("dwconv.cu", "resample.cu")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -52,8 +52,7 @@ def _source_digest():
 def _jobs():
     jobs = []
     for src in PLAIN_SOURCES:
-        if os.path.exists(os.path.join(CSRC, src)):
-            jobs.append((src, [], os.path.join(OBJ_DIR, src.replace(".cu", ".o"))))
+        jobs.append((src, [], os.path.join(OBJ_DIR, src.replace(".cu", ".o"))))
     for k in FILTER_WIDTHS:
         jobs.append(("dwconv_k.cu", ["-DPDW_K=%d" % k], os.path.join(OBJ_DIR, "dwconv_k%d.o" % k)))
     return jobs

@@ -1,0 +1,158 @@
+"""GPU parity of the composed path: SimpleGate / ConvBlock through the autograd Functions against
+the golden run of the unmodified reference (config 1) and the CPU oracle, plus size-independent
+properties at the benchmark's full tensor sizes."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close_16bit, assert_close_fp32, draw, golden
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+from pyramid_dwconv import ConvBlock  # noqa: E402
+from pyramidconvblock_b200 import ops  # noqa: E402
+from pyramidconvblock_b200.modules import SimpleGate  # noqa: E402
+
+
+def test_convblock_config1_matches_reference_golden():
+    """ConvBlock(64, k=9) fp32, x [2,32,32,64] seed 0, upstream grad seed 1, default init seed 0."""
+    g = golden("convblock_cfg1.npz")
+    torch.manual_seed(0)
+    m = ConvBlock(64, kernel_size=9).to(torch.float32).cuda()
+    (x,) = draw([(2, 32, 32, 64)], 0)
+    (go,) = draw([(2, 32, 32, 64)], 1)
+    xd = x.cuda().requires_grad_(True)
+    y = m(xd)
+    y.backward(go.cuda())
+    ops.check_device_status()
+    assert_close_fp32(y.detach().cpu().numpy(), g["y"], "y")
+    assert_close_fp32(xd.grad.cpu().numpy(), g["dx"], "dx")
+    for name, p in m.named_parameters():
+        assert_close_fp32(p.grad.cpu().numpy(), g["grad." + name], "grad " + name)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_convblock_16bit_against_fp32_oracle(dtype):
+    torch.manual_seed(0)
+    m = ConvBlock(64, kernel_size=13).to(dtype).cuda()
+    params = {k: v.detach().float().cpu() for k, v in m.state_dict().items()}
+    (x,) = draw([(2, 24, 40, 64)], 2)
+    (go,) = draw([(2, 24, 40, 64)], 3)
+    x, go = x.to(dtype), go.to(dtype)
+    y_ref, dx_ref, grads_ref = oracle.ref_block_forward_backward(x.float(), go.float(), params, dtype=torch.float32)
+    xd = x.cuda().requires_grad_(True)
+    y = m(xd)
+    y.backward(go.cuda())
+    ops.check_device_status()
+    # the block chains five 16-bit ops; each output is judged on the north-star bar against its
+    # own magnitude (atol scaled by the tensor's max so large-magnitude gradients are not failed
+    # by an absolute 2e-3)
+    def bar(a, e, what):
+        e = e.numpy()
+        assert_close_16bit(a.float().cpu().numpy(), e, what, rtol=2e-2, atol=2e-3 + 1e-2 * float(np.abs(e).max()))
+    bar(y.detach(), y_ref, "y")
+    bar(xd.grad, dx_ref, "dx")
+    for name, p in m.named_parameters():
+        bar(p.grad, grads_ref[name], "grad " + name)
+
+
+@pytest.mark.parametrize("scale_factor", [1.0, 0.5])
+def test_simple_gate_matches_oracle(scale_factor):
+    torch.manual_seed(1)
+    gate = SimpleGate(32, kernel_size=9, scale_factor=scale_factor).to(torch.float32).cuda()
+    w = gate.conv_spatial.weight.detach().cpu()
+    (x,) = draw([(2, 18, 22, 32)], 4)
+    (go,) = draw([(2, 18, 22, 16)], 5)
+    xr = x.double().requires_grad_(True)
+    wr = w.double().requires_grad_(True)
+    y_ref = oracle.torch_gate_branch(xr, wr, scale_factor)
+    y_ref.backward(go.double())
+    xd = x.cuda().requires_grad_(True)
+    y = gate(xd)
+    y.backward(go.cuda())
+    assert_close_fp32(y.detach().cpu().numpy(), y_ref.detach().numpy(), "y")
+    assert_close_fp32(xd.grad.cpu().numpy(), xr.grad.numpy(), "dx")
+    assert_close_fp32(gate.conv_spatial.weight.grad.cpu().numpy(), wr.grad.numpy(), "dw")
+
+
+def test_function_signature_and_dtypes():
+    """apply(input, weight, stride, padding, dilation, dtype) as in the reference; dX in the input's
+    dtype, dW in the weight's dtype, output in `dtype`."""
+    from pyramid_dwconv import DepthwiseConv2DFunction
+    x = torch.randn(1, 10, 10, 8, device="cuda", dtype=torch.float16, requires_grad=True)
+    w = torch.randn(5, 5, 8, device="cuda", dtype=torch.float16, requires_grad=True)
+    y = DepthwiseConv2DFunction.apply(x, w, (1, 1), (2, 2), (1, 1), torch.float16)
+    assert y.dtype == torch.float16 and y.shape == (1, 10, 10, 8)
+    y.sum().backward()
+    assert x.grad.dtype == torch.float16 and w.grad.dtype == torch.float16 and w.grad.shape == (5, 5, 8)
+    b = torch.zeros(8, device="cuda", dtype=torch.float16, requires_grad=True)
+    DepthwiseConv2DFunction.apply(x, w, 1, 2, 1, torch.float16, b).sum().backward()
+    assert torch.allclose(b.grad.float(), torch.full((8,), 100.0, device="cuda"))
+    with pytest.raises(RuntimeError):
+        ops.dwconv_forward(x.detach(), w.detach().float(), None, 1, 2, 1)
+
+
+# ---- size-independent properties at the benchmark sizes (no CPU oracle can run these in seconds) ----
+@pytest.mark.parametrize("k", [9, 13, 17])
+def test_full_size_adjoint_identities(k):
+    """<conv(x), g> == <x, dX(g)> == <w, dW(x, g)> on [16,128,128,256] fp16 inputs (config 2 shape),
+    evaluated in fp64 from the 16-bit outputs; and dbias == sum of g."""
+    B, H, W, C = 16, 128, 128, 256
+    gen = torch.Generator(device="cuda").manual_seed(k)
+    x = torch.randn((B, H, W, C), generator=gen, device="cuda").half()
+    g = torch.randn((B, H, W, C), generator=gen, device="cuda").half()
+    w = (torch.randn((k, k, C), generator=gen, device="cuda") / k).half()
+    y = ops.dwconv_forward(x, w, None, 1, k // 2, 1)
+    dx = ops.dwconv_backward_input(g, w, (H, W), 1, k // 2, 1)
+    dw, db = ops.dwconv_backward_weight(x, g, k, 1, k // 2, 1, with_bias=True, out_dtype=torch.float32)
+    ops.check_device_status()
+    lhs = (y.double() * g.double()).sum().item()
+    mid = (x.double() * dx.double()).sum().item()
+    rhs = (w.double() * dw.double()).sum().item()
+    scale = (y.double().pow(2).sum().sqrt() * g.double().pow(2).sum().sqrt()).item()
+    assert abs(lhs - mid) <= 2e-3 * scale * 1e-2 + 1e-3 * abs(lhs), (lhs, mid)
+    assert abs(lhs - rhs) <= 2e-3 * scale * 1e-2 + 1e-3 * abs(lhs), (lhs, rhs)
+    assert torch.allclose(db.double(), g.double().sum(dim=(0, 1, 2)), rtol=1e-4, atol=1e-2)
+
+
+def test_full_size_linearity_and_shift():
+    """conv(a*x1 + x2) == a*conv(x1) + conv(x2) up to 16-bit rounding, and a one-hot filter is a pure
+    shift (bit exact) on the config-5 per-GPU shape."""
+    B, H, W, C, k = 16, 96, 96, 256, 17
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x1 = torch.randn((B, H, W, C), generator=gen, device="cuda").bfloat16()
+    w = torch.zeros(k, k, C, device="cuda", dtype=torch.bfloat16)
+    w[2, 11, :] = 1
+    y = ops.dwconv_forward(x1, w, None, 1, k // 2, 1)
+    expect = torch.zeros_like(x1)
+    dy, dxs = 2 - k // 2, 11 - k // 2     # y[h,w] = x[h+dy, w+dxs]
+    expect[:, -dy:, :W - dxs, :] = x1[:, :H + dy, dxs:, :]
+    assert torch.equal(y, expect)
+    w = (torch.randn((k, k, C), generator=gen, device="cuda") / k).bfloat16()
+    x2 = torch.randn((B, H, W, C), generator=gen, device="cuda").bfloat16()
+    lhs = ops.dwconv_forward((2 * x1.float() + x2.float()).bfloat16(), w, None, 1, k // 2, 1).float()
+    rhs = 2 * ops.dwconv_forward(x1, w, None, 1, k // 2, 1).float() + ops.dwconv_forward(x2, w, None, 1, k // 2, 1).float()
+    assert (lhs - rhs).abs().max().item() <= 2e-2 * rhs.abs().max().item()
+
+
+@pytest.mark.parametrize("s", [64, 32, 16])
+def test_full_size_pool_upsample_properties(s):
+    """Config 4 shape [32,128,128,384] bf16: pooling conserves the mean, pool backward conserves the
+    sum of the gradient, upsample backward conserves it too, and <up(x), g> == <x, up_bwd(g)>."""
+    B, H, W, C = 32, 128, 128, 384
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = (torch.rand((B, H, W, C), generator=gen, device="cuda") * 2 - 1).bfloat16()
+    g = torch.randn((B, H, W, C), generator=gen, device="cuda").bfloat16()
+    p = ops.pool_forward(x, (s, s))
+    assert abs(p.double().mean().item() - x.double().mean().item()) < 1e-4
+    gs = g[:, :s, :s, :].contiguous()
+    pb = ops.pool_backward(gs, (H, W))
+    assert abs(pb.double().sum().item() - gs.double().sum().item()) <= 2e-3 * gs.double().abs().sum().item()
+    u = ops.upsample_forward(p, (H, W))
+    ub = ops.upsample_backward(g, (s, s))
+    assert abs(ub.double().sum().item() - g.double().sum().item()) <= 2e-3 * g.double().abs().sum().item()
+    lhs = (u.double() * g.double()).sum().item()
+    rhs = (p.double() * ub.double()).sum().item()
+    scale = (u.double().pow(2).sum().sqrt() * g.double().pow(2).sum().sqrt()).item()
+    assert abs(lhs - rhs) <= 1e-2 * scale * 1e-1 + 1e-2 * abs(lhs)
