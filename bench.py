@@ -1,0 +1,445 @@
+#!/usr/bin/env python
+"""Benchmark of the ConvBlock hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the one the baseline's metric is quoted on across 1/2/4/8 GPUs): the data-parallel
+training step of ``ConvBlock(dim=512, kernel_size=17)`` in bfloat16 on a GLOBAL NHWC batch
+[128,96,96,512] split evenly over the ranks (strong scaling): forward, backward with a given
+upstream gradient (dX and every parameter gradient) and one all-reduce of the parameter
+gradients.  Data are seeded synthetic tensors of that shape; weights are the module's default
+init.  One "step" is that whole pass over the rank's shard.
+
+Prints ONE JSON line (rank 0).  ``value`` is images/s of the whole job with inputs resident in
+HBM; ``e2e`` is the same metric through the public module API with the step's inputs copied
+from pinned host memory and the reduced gradients read back every step.  ``roofline`` covers the
+dominant kernel (the TMA-tiled depthwise convolution, which runs forward and input-gradient),
+timed live with CUDA events inside the timed region; ``kernels`` lists every C-ABI entry point
+the same way.  ``cpu_baseline`` is the reference's CPU path (torch ``F.conv2d(groups=C)`` +
+``adaptive_avg_pool2d`` + bilinear ``interpolate`` composition, from ``oracle/``) timed on the
+host cores on a bounded sample.  ``--impl reference`` times only that CPU path.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+import torch.distributed as dist
+
+GLOBAL_BATCH, HEIGHT, WIDTH, DIM, KSIZE = 128, 96, 96, 512, 17
+DTYPE = torch.bfloat16
+SEED = 4
+WORKLOAD = "ConvBlock(dim=512,k=17) bf16 data-parallel training step, global NHWC [128,96,96,512]"
+
+
+def valid_taps(n, k):
+    """Taps of a same-padded stride-1 filter that land inside an axis of length n, summed over
+    the axis: n*k - p*(p+1), p = k//2 (padding taps are not counted as work)."""
+    p = k // 2
+    return n * k - p * (p + 1)
+
+
+def conv_fmas(b, h, w, c, k):
+    return b * c * valid_taps(h, k) * valid_taps(w, k)
+
+
+def load_peaks():
+    """Roofline denominators: measured HBM copy bandwidth and the FP32 FMA peak at the measured
+    maximum SM clock (148 SMs x 128 lanes x 2 flop); fallback figures if the file is absent."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        peaks = {"hbm_gbs": float(m["hbm_gbs"]), "sm_max_mhz": float(m.get("sm_max_mhz", 1965.0)),
+                 "source": "measured"}
+    peaks["fp32_tflops"] = 148 * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
+    return peaks
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.lines = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v.strip() for v in vis.split(",") if v.strip()]
+        if local_rank < len(ids) and ids[local_rank].isdigit():
+            return int(ids[local_rank])
+    return local_rank
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU path of the reference (oracle/): used for cpu_baseline and for --impl reference
+# -------------------------------------------------------------------------------------------------
+def cpu_reference_step_fn(images):
+    """Builds the CPU step: ConvBlock(512,k=17) forward+backward on `images` images through the
+    torch composition of oracle/ (same dtype if the CPU ops support it, else float32)."""
+    from oracle import oracle
+    from pyramid_dwconv import ConvBlock
+    torch.manual_seed(SEED)
+    params = {k: v.detach() for k, v in ConvBlock(DIM, kernel_size=KSIZE).state_dict().items()}
+    g = torch.Generator().manual_seed(SEED)
+    x = torch.randn((images, HEIGHT, WIDTH, DIM), generator=g)
+    go = torch.randn((images, HEIGHT, WIDTH, DIM), generator=g)
+    dtype = DTYPE
+    try:
+        oracle.ref_block_forward_backward(x[:1, :8, :8], go[:1, :8, :8], params, dtype=dtype)
+    except RuntimeError:
+        dtype = torch.float32
+
+    def step():
+        oracle.ref_block_forward_backward(x, go, params, dtype=dtype)
+
+    return step, str(dtype).replace("torch.", "")
+
+
+def time_cpu_reference(budget_s=15.0, max_images=8):
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    step, dtype = cpu_reference_step_fn(1)
+    step()   # warm-up (thread pool, allocations)
+    t0 = time.perf_counter()
+    step()
+    t1 = time.perf_counter() - t0
+    images = max(1, min(max_images, int(budget_s / max(t1, 1e-3))))
+    reps = 1
+    if images > 1:
+        step, dtype = cpu_reference_step_fn(images)
+        step()
+        t0 = time.perf_counter()
+        step()
+        t1 = time.perf_counter() - t0
+    return {"value": images * reps / t1, "unit": "images/s", "cores": cores, "kind": "port",
+            "sample": "%d image(s) [96,96,512] fwd+bwd in %s, torch CPU composition (oracle/), %.2f s"
+                      % (images, dtype, t1)}
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    images = 2
+    step, dtype = cpu_reference_step_fn(images)
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = images * steps / dt
+    sample = "%d images [96,96,512] per step, %d steps, %s, torch CPU composition (oracle/)" % (images, steps, dtype)
+    print(json.dumps({
+        "impl": "reference", "metric": "convblock_train_images_per_s", "value": value, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# -------------------------------------------------------------------------------------------------
+# GPU arm
+# -------------------------------------------------------------------------------------------------
+def extra_sweeps(device):
+    """Single-GPU side measurements the baseline also names: depthwise conv forward on fp16
+    [16,128,128,256] for k = 9/13/17 and the ConvBlock(256,k) fp16 forward+backward."""
+    from pyramid_dwconv import ConvBlock
+    from pyramidconvblock_b200 import ops
+    peaks = load_peaks()
+    out = {}
+
+    def timed(fn, n=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / n
+
+    gen = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn((16, 128, 128, 256), generator=gen, device=device).half()
+    go = torch.randn((16, 128, 128, 256), generator=gen, device=device).half()
+    for k in (9, 13, 17):
+        w = (torch.randn((k, k, 256), generator=gen, device=device) / k).half()
+        b = (torch.randn((256,), generator=gen, device=device) * 0.1).half()
+        fma = conv_fmas(16, 128, 128, 256, k)
+        rec = {}
+        for name, fn in (("fwd", lambda: ops.dwconv_forward(x, w, b, 1, k // 2, 1)),
+                         ("bwd_input", lambda: ops.dwconv_backward_input(go, w, (128, 128), 1, k // 2, 1)),
+                         ("bwd_weight_bias", lambda: ops.dwconv_backward_weight(x, go, k, 1, k // 2, 1, with_bias=True))):
+            ms = timed(fn)
+            rec[name] = {"ms": round(ms, 4), "frac_fp32_peak": round(2 * fma / (ms * 1e-3) / 1e12 / peaks["fp32_tflops"], 4)}
+        torch.manual_seed(0)
+        m = ConvBlock(256, kernel_size=k).to(torch.float16).to(device)
+        xg = x.clone().requires_grad_(True)
+
+        def block_step():
+            xg.grad = None
+            for p in m.parameters():
+                p.grad = None
+            m(xg).backward(go)
+
+        rec["convblock256_fwd_bwd_ms"] = round(timed(block_step, n=5, warm=2), 4)
+        out["k%d" % k] = rec
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the k=9/13/17 side sweeps")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    if args.warmup < 3:
+        args.warmup = 3
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    if world != args.gpus and rank == 0:
+        print("note: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (args.gpus, world), file=sys.stderr)
+
+    from pyramid_dwconv import ConvBlock
+    from pyramidconvblock_b200 import check_device_status, ops
+    from pyramidconvblock_b200.parallel import GradientBucket, shard_batch, train_step
+
+    lo, hi = shard_batch(GLOBAL_BATCH, rank, world)
+    local_b = hi - lo
+    torch.manual_seed(SEED)
+    model = ConvBlock(DIM, kernel_size=KSIZE).to(DTYPE).to(device)
+    bucket = GradientBucket(model.parameters())
+    gen = torch.Generator(device=device).manual_seed(SEED + 1000 * rank)
+    x = torch.randn((local_b, HEIGHT, WIDTH, DIM), generator=gen, device=device).to(DTYPE).requires_grad_(True)
+    gout = torch.randn((local_b, HEIGHT, WIDTH, DIM), generator=gen, device=device).to(DTYPE)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident arm ----------------------------------------------------------------------
+    for _ in range(args.warmup):
+        train_step(model, bucket, x, gout)
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ops.KernelTimer() as timer:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            train_step(model, bucket, x, gout)
+        e1.record()
+        barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_per_step = ms_total / args.steps
+    value = GLOBAL_BATCH / (ms_per_step * 1e-3)
+    check_device_status(device)
+    summary = timer.summary()
+    launches = timer.kernel_launches()
+
+    # ---- end-to-end arm: host buffers in, reduced gradients out, every step ----------------------
+    x_host = x.detach().cpu().pin_memory()
+    g_host = gout.cpu().pin_memory()
+    grads_host = torch.empty(bucket.numel, dtype=torch.float32).pin_memory()
+    x_dev = torch.empty_like(x_host, device=device)
+    g_dev = torch.empty_like(g_host, device=device)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        g_dev.copy_(g_host, non_blocking=True)
+        xin = x_dev.detach().requires_grad_(True)
+        train_step(model, bucket, xin, g_dev)
+        grads_host.copy_(bucket.flat, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()   # the caller holds the result on the host
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    h2d = x_host.numel() * x_host.element_size() + g_host.numel() * g_host.element_size()
+    d2h = grads_host.numel() * grads_host.element_size()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel and per-entry-point table ---------------------------------
+    peaks = load_peaks()
+    half = DIM // 2
+    es = 2
+    kernels = {}
+    for (label, shape), rec in sorted(summary.items()):
+        avg_ms = rec["ms"] / rec["calls"]
+        entry = {"calls": rec["calls"], "kernels": rec["kernels"], "avg_ms": round(avg_ms, 4)}
+        if label.startswith("dwconv"):
+            b, h, w, c, k = shape
+            fl = 2 * conv_fmas(b, h, w, c, k)
+            entry["tflops"] = round(fl / (avg_ms * 1e-3) / 1e12, 3)
+            entry["frac_fp32_peak"] = round(entry["tflops"] / peaks["fp32_tflops"], 4)
+        elif label in ("pool_fwd", "pool_bwd", "upsample_fwd", "upsample_bwd"):
+            b, h, w, c, oh, ow = shape
+            byts = b * c * es * (h * w + oh * ow)
+            entry["gbs"] = round(byts / (avg_ms * 1e-3) / 1e9, 1)
+            entry["frac_hbm_peak"] = round(entry["gbs"] / peaks["hbm_gbs"], 4)
+        elif label in ("gate_fwd", "gate_bwd"):
+            pixels, c = shape
+            byts = pixels * c * es * (1.5 if label == "gate_fwd" else 2.5)
+            entry["gbs"] = round(byts / (avg_ms * 1e-3) / 1e9, 1)
+            entry["frac_hbm_peak"] = round(entry["gbs"] / peaks["hbm_gbs"], 4)
+        kernels["%s%s" % (label, list(shape))] = entry
+
+    # dominant kernel: the tiled convolution on the full-resolution gate (forward + input gradient)
+    dom_shape = (local_b, HEIGHT, WIDTH, half, KSIZE)
+    dom = [summary[(l, dom_shape)] for l in ("dwconv_fwd", "dwconv_bwd_input") if (l, dom_shape) in summary]
+    dom_calls = sum(r["calls"] for r in dom)
+    dom_ms = sum(r["ms"] for r in dom) / max(dom_calls, 1)
+    dom_flops = 2 * conv_fmas(*dom_shape)
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12 if dom_calls else None
+    # DRAM traffic of one launch from the ncu capture summarised in profiles/ (bytes per image of
+    # [96,96,256] bf16, scaled by the images one launch processes); None until captured.
+    traffic_per_image = TRAFFIC_BYTES_PER_IMAGE
+    roofline = {
+        "kernel": "dwconv_tiled_kernel<bf16,K=17> (forward and input gradient, gate 0: [%d,96,96,256])" % local_b,
+        "bound": "fp32_fma", "achieved": round(achieved, 3) if achieved else None,
+        "peak": round(peaks["fp32_tflops"], 2), "unit": "TFLOP/s",
+        "frac": round(achieved / peaks["fp32_tflops"], 4) if achieved else None,
+        "peak_source": "148 SMs x 128 FP32 lanes x 2 x sm_max_mhz of MEASURED_PEAKS.json (%s); tensor cores do not "
+                       "apply to a depthwise convolution" % peaks["source"],
+        "flops_per_launch": dom_flops, "avg_launch_ms": round(dom_ms, 4), "launches": dom_calls,
+        "hbm_bytes_per_launch": 2 * local_b * HEIGHT * WIDTH * half * es,
+        "hbm_time_at_peak_ms": round(2 * local_b * HEIGHT * WIDTH * half * es / (peaks["hbm_gbs"] * 1e9) * 1e3, 4),
+        "traffic": traffic_per_image * local_b if traffic_per_image else None,
+    }
+    total_conv_flops = 0
+    for (b, h, w) in ((local_b, HEIGHT, WIDTH), (local_b, HEIGHT // 2, WIDTH // 2)):
+        total_conv_flops += 3 * 2 * conv_fmas(b, h, w, half, KSIZE)
+    step_roofline_ms = total_conv_flops / (peaks["fp32_tflops"] * 1e12) * 1e3
+
+    result = {
+        "metric": "convblock_train_images_per_s", "value": round(value, 2), "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": local_b,
+                   "parallelism": "dp%d" % world,
+                   "l2": "inputs larger than L2 (x and grad of %d MB each per GPU)" % (x.numel() * 2 // 2 ** 20)},
+        "e2e": {"value": round(GLOBAL_BATCH / (e2e_ms * 1e-3), 2), "unit": "images/s", "ms_per_step": round(e2e_ms, 4),
+                "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": roofline,
+        "step_fraction_of_conv_roofline": round(step_roofline_ms / ms_per_step, 4),
+        "kernels": kernels,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = time_cpu_reference()
+    if world == 1 and not args.no_extra:
+        result["extra"] = extra_sweeps(device)
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one dwconv_tiled_kernel launch per image of [96,96,256] bf16, k=17,
+# from the ncu capture summarised under profiles/; None until that capture exists.
+TRAFFIC_BYTES_PER_IMAGE = None
+
+if __name__ == "__main__":
+    main()

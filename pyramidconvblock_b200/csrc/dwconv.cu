@@ -12,7 +12,7 @@ thread_local int g_last_cuda_error = 0;
 // ---------------------------------------------------------------------------------------------
 // Library-wide helpers
 // ---------------------------------------------------------------------------------------------
-static int g_tuning[3] = {0, 16, 0};
+static int g_tuning[3] = {1, 16, 0};
 int tuning(int key) { return g_tuning[key]; }
 
 int sm_count() {

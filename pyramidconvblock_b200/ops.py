@@ -15,6 +15,55 @@ _DTYPES = {torch.float32: _lib.PDW_F32, torch.float16: _lib.PDW_F16, torch.bfloa
 _status_words = {}
 
 
+class KernelTimer:
+    """While installed (``with KernelTimer() as t``), every C-ABI call is bracketed by CUDA events on
+    the stream it launches on and counted.  ``summary()`` (after a synchronize) gives, per
+    (entry point, shape), the number of calls, kernels launched and total device milliseconds."""
+
+    def __init__(self):
+        self.records = []
+
+    def __enter__(self):
+        global _timer
+        self._prev = _timer
+        _timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = self._prev
+
+    def summary(self):
+        out = {}
+        for label, shape, kernels, e0, e1 in self.records:
+            rec = out.setdefault((label, shape), {"calls": 0, "kernels": 0, "ms": 0.0})
+            rec["calls"] += 1
+            rec["kernels"] += kernels
+            rec["ms"] += e0.elapsed_time(e1)
+        return out
+
+    def kernel_launches(self):
+        return sum(r[2] for r in self.records)
+
+
+_timer = None
+
+
+def _call(label, shape, kernels, device, fn):
+    """Runs one C-ABI call; brackets it with events when a KernelTimer is installed."""
+    t = _timer
+    if t is None:
+        return fn()
+    stream = torch.cuda.current_stream(device)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    rc = fn()
+    e1.record(stream)
+    t.records.append((label, shape, kernels, e0, e1))
+    return rc
+
+
 def _dtype_code(t):
     try:
         return _DTYPES[t.dtype]
@@ -104,8 +153,9 @@ def dwconv_forward(x, weight, bias=None, stride=1, padding=0, dilation=1):
     y = torch.empty((B, OH, OW, C), device=x.device, dtype=x.dtype)
     g = _geom(x.shape, k, stride, padding, dilation)
     with torch.cuda.device(x.device):
-        rc = _lib.lib().pdw_dwconv_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), ctypes.byref(g), _dtype_code(x),
-                                       _ptr(status_word(x.device)), _stream(x))
+        rc = _call("dwconv_fwd", (B, H, W, C, k[0]), 1, x.device, lambda: _lib.lib().pdw_dwconv_fwd(
+            _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), ctypes.byref(g), _dtype_code(x),
+            _ptr(status_word(x.device)), _stream(x)))
     _lib.check(rc, "pdw_dwconv_fwd")
     return y
 
@@ -124,9 +174,9 @@ def dwconv_backward_input(grad_out, weight, input_hw, stride=1, padding=0, dilat
     dx = torch.empty((B, H, W, C), device=grad_out.device, dtype=grad_out.dtype)
     g = _geom((B, H, W, C), k, stride, padding, dilation)
     with torch.cuda.device(grad_out.device):
-        rc = _lib.lib().pdw_dwconv_bwd_input(_ptr(grad_out), _ptr(weight), _ptr(dx), ctypes.byref(g),
-                                             _dtype_code(grad_out), _ptr(status_word(grad_out.device)),
-                                             _stream(grad_out))
+        rc = _call("dwconv_bwd_input", (B, H, W, C, k[0]), 1, dx.device, lambda: _lib.lib().pdw_dwconv_bwd_input(
+            _ptr(grad_out), _ptr(weight), _ptr(dx), ctypes.byref(g), _dtype_code(grad_out),
+            _ptr(status_word(grad_out.device)), _stream(grad_out)))
     _lib.check(rc, "pdw_dwconv_bwd_input")
     return dx
 
@@ -158,8 +208,10 @@ def dwconv_backward_weight(x, grad_out, kernel_size, stride=1, padding=0, dilati
     with torch.cuda.device(x.device):
         need = L.pdw_dwconv_bwd_weight_workspace(ctypes.byref(g), _dtype_code(x))
         ws = torch.empty((max(need, 16),), device=x.device, dtype=torch.uint8)
-        rc = L.pdw_dwconv_bwd_weight(_ptr(x), _ptr(grad_out), _ptr(dw), _ptr(dbias), ctypes.byref(g), _dtype_code(x),
-                                     out_fp32, _ptr(ws), need, _ptr(status_word(x.device)), _stream(x))
+        rc = _call("dwconv_bwd_weight", (B, H, W, C, k[0]), 2 if need else 1, x.device,
+                   lambda: L.pdw_dwconv_bwd_weight(
+                       _ptr(x), _ptr(grad_out), _ptr(dw), _ptr(dbias), ctypes.byref(g), _dtype_code(x), out_fp32,
+                       _ptr(ws), need, _ptr(status_word(x.device)), _stream(x)))
     _lib.check(rc, "pdw_dwconv_bwd_weight")
     return dw, dbias
 
@@ -170,7 +222,8 @@ def _resample(fn_name, src, out_shape, H, W, OH, OW):
     dst = torch.empty(out_shape, device=src.device, dtype=src.dtype)
     B, C = src.shape[0], src.shape[3]
     with torch.cuda.device(src.device):
-        rc = getattr(_lib.lib(), fn_name)(_ptr(src), _ptr(dst), B, H, W, C, OH, OW, _dtype_code(src), _stream(src))
+        rc = _call(fn_name[4:], (B, H, W, C, OH, OW), 1, src.device, lambda: getattr(_lib.lib(), fn_name)(
+            _ptr(src), _ptr(dst), B, H, W, C, OH, OW, _dtype_code(src), _stream(src)))
     _lib.check(rc, fn_name)
     return dst
 
@@ -213,8 +266,8 @@ def gate_forward(conv_out, inv_scale):
     pixels = conv_out.numel() // C
     y = torch.empty(conv_out.shape[:-1] + (C // 2,), device=conv_out.device, dtype=conv_out.dtype)
     with torch.cuda.device(conv_out.device):
-        rc = _lib.lib().pdw_gate_fwd(_ptr(conv_out), _ptr(y), pixels, C, float(inv_scale), _dtype_code(conv_out),
-                                     _stream(conv_out))
+        rc = _call("gate_fwd", (pixels, C), 1, conv_out.device, lambda: _lib.lib().pdw_gate_fwd(
+            _ptr(conv_out), _ptr(y), pixels, C, float(inv_scale), _dtype_code(conv_out), _stream(conv_out)))
     _lib.check(rc, "pdw_gate_fwd")
     return y
 
@@ -226,8 +279,9 @@ def gate_backward(conv_out, grad_y, inv_scale):
     pixels = conv_out.numel() // C
     ga = torch.empty_like(conv_out)
     with torch.cuda.device(conv_out.device):
-        rc = _lib.lib().pdw_gate_bwd(_ptr(conv_out), _ptr(grad_y), _ptr(ga), pixels, C, float(inv_scale),
-                                     _dtype_code(conv_out), _stream(conv_out))
+        rc = _call("gate_bwd", (pixels, C), 1, conv_out.device, lambda: _lib.lib().pdw_gate_bwd(
+            _ptr(conv_out), _ptr(grad_y), _ptr(ga), pixels, C, float(inv_scale), _dtype_code(conv_out),
+            _stream(conv_out)))
     _lib.check(rc, "pdw_gate_bwd")
     return ga
 
