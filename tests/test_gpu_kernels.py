@@ -31,13 +31,12 @@ def rounded(t, dtype):
 @pytest.fixture(autouse=True)
 def _reset_tuning_and_check_status():
     L = _lib.lib()
-    L.pdw_set_tuning(0, 0)
-    L.pdw_set_tuning(1, 16)
-    L.pdw_set_tuning(2, 0)
+    defaults = ((0, 1), (1, 16), (2, 0))
+    for key, value in defaults:
+        L.pdw_set_tuning(key, value)
     yield
-    L.pdw_set_tuning(0, 0)
-    L.pdw_set_tuning(1, 16)
-    L.pdw_set_tuning(2, 0)
+    for key, value in defaults:
+        L.pdw_set_tuning(key, value)
     ops.check_device_status()
 
 
@@ -75,9 +74,13 @@ def run_conv_case(B, H, W, C, k, dtype, seed, stride=1, padding=None, dilation=1
         assert_close_16bit(db.float().cpu().numpy(), db_ref, "dbias", atol=2e-3 + 4e-3 * np.abs(db_ref).max())
 
 
+@pytest.mark.parametrize("math", [1, 0])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("k", [3, 5, 7, 9, 11, 13, 15, 17])
-def test_dwconv_tiled_all_widths(k, dtype):
+def test_dwconv_tiled_all_widths(k, dtype, math):
+    if dtype == torch.float32 and math == 0:
+        pytest.skip("fp32 has a single arithmetic form")
+    _lib.lib().pdw_set_tuning(0, math)
     run_conv_case(2, 21, 19, 16, k, dtype, seed=100 + k)
 
 
