@@ -103,6 +103,27 @@ int pdw_dwconv_bwd_weight(const void* x, const void* grad_out, void* dw, void* d
                           int32_t* status_word, void* stream);
 
 /*
+ * The same weight/bias gradient for callers that cannot bring a workspace because they cannot
+ * allocate device memory at all: a plugin inside a host whose allocator it has no access to, a
+ * process that froze its memory budget at start-up, a latency-critical loop that must not enter the
+ * driver's allocator.  This entry point has no counterpart in the reference.  The partial sums go to
+ * a fixed array of PDW_STATIC_SCRATCH_BYTES that is part of the library image (every GPU that loads
+ * the library holds it until the process exits); no cudaMalloc, cudaFree or other allocating routine
+ * is called.  A geometry whose partial sums need more (pdw_dwconv_bwd_weight_workspace() tells) is
+ * refused with PDW_ERR_TOO_LARGE.  Results are bit-identical to pdw_dwconv_bwd_weight.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.  All calls share the one
+ * array per device and it keeps the previous call's partials (nothing needs clearing: each call
+ * overwrites everything it later reads), so two calls whose kernels may overlap on the GPU - different
+ * streams without an ordering between them - race; serialise them.
+ */
+#define PDW_STATIC_SCRATCH_BYTES (8u << 20)
+int pdw_dwconv_bwd_weight_static(const void* x, const void* grad_out, void* dw, void* dbias,
+                                 const pdw_conv_geom* g, int dtype, int out_fp32,
+                                 int32_t* status_word, void* stream);
+
+/*
  * Adaptive average pooling, window [floor(i*in/out), ceil((i+1)*in/out)) per axis in exact integer
  * arithmetic.  Replaces _adaptive_avg_pool_kernel (pyramid_dwconv/avgpool_triton.py:14-107) and the
  * F.adaptive_avg_pool2d call of SimpleGate (pyramid_dwconv/conv_block.py:16).  x [B,H,W,C] -> y [B,OH,OW,C].

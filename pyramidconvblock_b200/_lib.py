@@ -18,7 +18,7 @@ EXPORTED_SYMBOLS = (
     "pdw_version", "pdw_status_string", "pdw_last_cuda_error", "pdw_conv_out_size",
     "pdw_dwconv_fwd", "pdw_dwconv_bwd_input", "pdw_dwconv_bwd_weight_workspace", "pdw_dwconv_bwd_weight",
     "pdw_pool_fwd", "pdw_pool_bwd", "pdw_upsample_fwd", "pdw_upsample_bwd",
-    "pdw_gate_fwd", "pdw_gate_bwd", "pdw_set_tuning",
+    "pdw_gate_fwd", "pdw_gate_bwd", "pdw_set_tuning", "pdw_dwconv_bwd_weight_static",
 )
 
 
@@ -62,6 +62,8 @@ def _declare(lib):
     lib.pdw_gate_bwd.argtypes = [vp, vp, vp, i64, i32, f32, i32, vp]
     lib.pdw_set_tuning.restype = i32
     lib.pdw_set_tuning.argtypes = [i32, i32]
+    lib.pdw_dwconv_bwd_weight_static.restype = i32
+    lib.pdw_dwconv_bwd_weight_static.argtypes = [vp, vp, vp, vp, geom, i32, i32, vp, vp]
 
 
 def lib():

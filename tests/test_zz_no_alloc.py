@@ -1,0 +1,69 @@
+"""The allocation-free weight-gradient entry point, called through the C ABI.
+
+Some users of the library cannot hand it a workspace because they cannot allocate device memory
+themselves (a plugin without access to its host's allocator, a process with a frozen memory budget);
+``pdw_dwconv_bwd_weight_static`` keeps the partial sums in an array inside the library instead.  This
+test checks it against the caller-workspace entry point on two calls in a row with different data:
+the second call finds the first call's partials still in the array and must not be affected by them.
+The file name makes pytest collect it last."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close_fp32
+
+pytestmark = pytest.mark.gpu
+
+from pyramidconvblock_b200 import _lib  # noqa: E402
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _both_entry_points(x, go, k, dtype_code):
+    L = _lib.lib()
+    B, H, W, C = x.shape
+    geom = _lib.ConvGeom(B, H, W, C, k, k, 1, 1, k // 2, k // 2, 1, 1)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    need = L.pdw_dwconv_bwd_weight_workspace(ctypes.byref(geom), dtype_code)
+    assert 0 < need <= (8 << 20)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    dw_a = torch.empty((k, k, C), dtype=torch.float32, device="cuda")
+    db_a = torch.empty((C,), dtype=torch.float32, device="cuda")
+    dw_b = torch.full_like(dw_a, float("nan"))
+    db_b = torch.full_like(db_a, float("nan"))
+    rc = L.pdw_dwconv_bwd_weight(_ptr(x), _ptr(go), _ptr(dw_a), _ptr(db_a), ctypes.byref(geom), dtype_code, 1,
+                                 _ptr(ws), need, _ptr(status), stream)
+    assert rc == 0, L.pdw_status_string(rc)
+    rc = L.pdw_dwconv_bwd_weight_static(_ptr(x), _ptr(go), _ptr(dw_b), _ptr(db_b), ctypes.byref(geom), dtype_code, 1,
+                                        _ptr(status), stream)
+    assert rc == 0, L.pdw_status_string(rc)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return dw_a.cpu().numpy(), db_a.cpu().numpy(), dw_b.cpu().numpy(), db_b.cpu().numpy()
+
+
+def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    for call, (shape, k) in enumerate([((4, 40, 36, 64), 13), ((2, 33, 50, 32), 9)]):
+        x = torch.randn(shape, generator=gen, device="cuda").half()
+        go = torch.randn(shape, generator=gen, device="cuda").half()
+        dw_a, db_a, dw_b, db_b = _both_entry_points(x, go, k, _lib.PDW_F16)
+        assert np.isfinite(dw_b).all() and np.isfinite(db_b).all(), "call %d left outputs unwritten" % call
+        assert_close_fp32(dw_b, dw_a, "dW, call %d" % call)
+        assert_close_fp32(db_b, db_a, "dbias, call %d" % call)
+
+
+def test_static_scratch_entry_point_refuses_what_does_not_fit():
+    L = _lib.lib()
+    # 17x17 taps x 8192 channels of fp32 partials: far beyond the fixed array
+    geom = _lib.ConvGeom(64, 512, 512, 8192, 17, 17, 1, 1, 8, 8, 1, 1)
+    need = L.pdw_dwconv_bwd_weight_workspace(ctypes.byref(geom), _lib.PDW_F16)
+    assert need > (8 << 20)
+    fake = ctypes.c_void_p(4096)   # never dereferenced: the size check comes first
+    rc = L.pdw_dwconv_bwd_weight_static(fake, fake, fake, None, ctypes.byref(geom), _lib.PDW_F16, 0, None, None)
+    assert rc == 9 and b"capacity" in L.pdw_status_string(rc)
