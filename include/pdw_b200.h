@@ -172,7 +172,9 @@ int pdw_gate_bwd(const void* conv_out, const void* grad_y, void* grad_conv_out, 
  * Experiment hook, not part of the reference surface: selects between equivalent inner-loop
  * code paths of the tiled convolution kernels (key 0: arithmetic form for 16-bit inputs,
  * 0 = packed-pair FP32 FMA after conversion, 1 = mixed-precision FMA on the 16-bit operands;
- * key 1: channels per thread block tile, 16 or 32; key 2: force the untiled kernels when 1).
+ * key 1: channels per thread block tile, 16 or 32; key 2: force the untiled kernels when 1;
+ * keys 3/4 and 5/6: force the tile rows/columns of the forward and of the weight-gradient kernel,
+ * 0 = chosen by the library).
  * Results are identical for every setting.  Returns the previous value, or -1 for a bad key.
  */
 int pdw_set_tuning(int key, int value);

@@ -50,8 +50,8 @@ static int wgrad_entry(const WgradArgs& a) {
 static size_t wgrad_workspace(int B, int OH, int OW, int C, int KH, int dtype) {
     WgradPlan plan{};
     const int esize = (int)dtype_size(dtype);
-    const bool ok = tuning(1) == 32 ? plan_wgrad<32>(B, OH, OW, C, KH, PDW_K, esize, sm_count(), &plan)
-                                    : plan_wgrad<16>(B, OH, OW, C, KH, PDW_K, esize, sm_count(), &plan);
+    const bool ok = tuning(1) == 32 ? plan_wgrad<32, PDW_K>(B, OH, OW, C, KH, esize, sm_count(), &plan)
+                                    : plan_wgrad<16, PDW_K>(B, OH, OW, C, KH, esize, sm_count(), &plan);
     return ok ? plan.workspace_bytes : 0;
 }
 

@@ -44,6 +44,7 @@ struct TiledParams {
     const void* w;
     const void* bias;
     void* out;
+    int H, W;             // input extents (rows/columns outside are the zero padding)
     int OH, OW, C;
     int KH, pad_h, pad_w, flip;
     int TH, TWc;          // output tile of one thread block
@@ -118,17 +119,28 @@ dwconv_tiled_kernel(const __grid_constant__ CUtensorMap tmap, const TiledParams 
         bias2 = E::unpack(*reinterpret_cast<const pair_t*>(static_cast<const T*>(p.bias) + c));
     const int row_bytes = p.cols * PIXB;
 
-    for (int item = warp; item < p.n_items; item += kFwdThreads / 32) {
-        const int strip = item % p.n_strips;
-        const int orow = (item / p.n_strips) * RL + rl;
+    // Only the part of the tile that holds output pixels is computed (ragged last tiles).
+    const int oh_tile = th * p.TH, ow_tile = tw * p.TWc;
+    const int groups = min(p.TH / RL, (p.OH - oh_tile + RL - 1) / RL);
+    const int strips = min(p.n_strips, (p.OW - ow_tile + kStrip - 1) / kStrip);
+    const int n_items = groups * strips;
+    for (int item = warp; item < n_items; item += kFwdThreads / 32) {
+        const int strip = item % strips;
+        const int grp = item / strips;
+        const int orow = grp * RL + rl;
         const int ocol = strip * kStrip;
         float2 acc[kStrip];
 #pragma unroll
         for (int o = 0; o < kStrip; ++o) acc[o] = bias2;
 
-        const unsigned char* xp = xs + (size_t)orow * row_bytes + ocol * PIXB + cp * (int)sizeof(pair_t);
-        const wreg_t* wp = ws + cp;
-        for (int kh = 0; kh < p.KH; ++kh) {
+        // Filter rows that can touch image rows for any of this warp's RL output rows; rows that only
+        // see the zero padding above or below the image are skipped (warp-uniform bounds).
+        const int oh_first = oh_tile + grp * RL;
+        const int kh_lo = max(0, p.pad_h - (oh_first + RL - 1));
+        const int kh_hi = min(p.KH, p.H + p.pad_h - oh_first);
+        const unsigned char* xp = xs + (size_t)(orow + kh_lo) * row_bytes + ocol * PIXB + cp * (int)sizeof(pair_t);
+        const wreg_t* wp = ws + cp + kh_lo * K * CPL;
+        for (int kh = kh_lo; kh < kh_hi; ++kh) {
             wreg_t wr[K];
 #pragma unroll
             for (int kw = 0; kw < K; ++kw) wr[kw] = wp[kw * CPL];
@@ -154,9 +166,9 @@ dwconv_tiled_kernel(const __grid_constant__ CUtensorMap tmap, const TiledParams 
             wp += K * CPL;
         }
 
-        const int oh = th * p.TH + orow;
+        const int oh = oh_tile + orow;
         if (oh < p.OH && c < p.C) {
-            const int ow0 = tw * p.TWc + ocol;
+            const int ow0 = ow_tile + ocol;
             T* orow_ptr = static_cast<T*>(p.out) + (((size_t)b * p.OH + oh) * p.OW + ow0) * p.C + c;
 #pragma unroll
             for (int o = 0; o < kStrip; ++o) {
@@ -166,43 +178,73 @@ dwconv_tiled_kernel(const __grid_constant__ CUtensorMap tmap, const TiledParams 
     }
 }
 
-// Picks the thread-block tile: as little padding waste at the image edges and as few idle warps
-// as possible, then the larger tile (smaller halo share).  Returns false if nothing fits.
+// Tile shapes in order of preference, as measured on B200 for k = 9/13/17 on 48..128-pixel images:
+// 32x32 (smallest halo share that still lets two blocks share an SM) down to tiles for tiny images.
+struct TileShape { int th, tw; };
+constexpr TileShape kTilePreference[] = {{32, 32}, {16, 64}, {24, 32}, {16, 48}, {16, 32}, {32, 16},
+                                         {16, 16}, {8, 32},  {8, 16},  {4, 16}};
+
+// Picks the thread-block tile for the forward / input-gradient kernel: the first shape of the
+// preference list that fits two blocks per SM, wastes (almost) no warp rounds or edge items, and
+// still yields at least three blocks per SM slot (small problems want small tiles); failing the last
+// condition, the efficient shape with the most blocks.
 template <int CT>
 inline bool plan_fwd_tile(int OH, int OW, int KH, int K, int esize, int wreg_bytes, int n_batch_ct, int sms,
                           TiledParams* p, int* smem_bytes) {
     constexpr int CPL = CT / 2, RL = 32 / CPL;
     const int pixb = CT * esize;
-    double best = -1.0;
-    for (int TH = RL; TH <= 64; TH += RL) {
-        for (int TWc = kStrip; TWc <= 128; TWc += kStrip) {
-            const int rows = TH + KH - 1;
-            int cols = TWc + K - 1;
-            if (RL > 1 && (cols % 2) == 0) cols++;
-            if (rows > 256 || cols > 256) continue;
-            const int smem = 128 + round_up(rows * cols * pixb, 128) + KH * K * CPL * wreg_bytes;
-            if (smem > kSmemMax) continue;
-            const int tiles_h = ceil_div(OH, TH), tiles_w = ceil_div(OW, TWc);
-            const double eff_sp = (double)OH * OW / ((double)tiles_h * TH * tiles_w * TWc);
-            const int items = (TH / RL) * (TWc / kStrip);
-            const int warps = kFwdThreads / 32;
-            const double eff_w = (double)items / (ceil_div(items, warps) * warps);
-            const int per_sm = smem <= kSmemPerCta2 ? 2 : 1;
-            const double waves = (double)tiles_h * tiles_w * n_batch_ct / ((double)per_sm * sms);
-            const double eff_wave = waves / (double)(long long)(waves + 0.999999);
-            const double halo = (double)TH * TWc / ((double)rows * cols);
-            const double occ = per_sm == 2 ? 1.0 : 0.85;
-            const double score = eff_sp * eff_w * eff_wave * occ * (0.9 + 0.1 * halo);
-            if (score > best) {
-                best = score;
-                p->TH = TH; p->TWc = TWc; p->rows = rows; p->cols = cols;
-                p->tiles_h = tiles_h; p->tiles_w = tiles_w;
-                p->n_strips = TWc / kStrip; p->n_items = items;
-                *smem_bytes = smem;
+    const int force_th = tuning(3), force_tw = tuning(4);
+    struct Cand { int th, tw, rows, cols, smem, tiles_h, tiles_w; double eff, blocks; bool two; };
+    Cand cands[16];
+    int n = 0;
+    double best_eff = 0.0;
+    auto consider = [&](int TH, int TWc) {
+        if (TH % RL != 0 || TWc % kStrip != 0) return;
+        const int rows = TH + KH - 1;
+        int cols = TWc + K - 1;
+        if (RL > 1 && (cols % 2) == 0) cols++;
+        if (rows > 256 || cols > 256) return;
+        const int smem = 128 + round_up(rows * cols * pixb, 128) + KH * K * CPL * wreg_bytes;
+        if (smem > kSmemMax) return;
+        const int tiles_h = ceil_div(OH, TH), tiles_w = ceil_div(OW, TWc);
+        // Items (RL rows x 16 columns) of full / last-row / last-column / corner tiles; items without
+        // output pixels are not computed, so edge waste only counts at item granularity.
+        const int warps = kFwdThreads / 32;
+        const int g_full = TH / RL, g_last = ceil_div(OH - (tiles_h - 1) * TH, RL);
+        const int s_full = TWc / kStrip, s_last = ceil_div(OW - (tiles_w - 1) * TWc, kStrip);
+        double work = 0.0, slots = 0.0;
+        for (int ih = 0; ih < 2; ++ih) {
+            for (int iw = 0; iw < 2; ++iw) {
+                const double count = (ih ? 1 : tiles_h - 1) * (double)(iw ? 1 : tiles_w - 1);
+                const int it = (ih ? g_last : g_full) * (iw ? s_last : s_full);
+                work += count * it;
+                slots += count * ceil_div(it, warps) * warps;
             }
         }
+        const bool two = smem <= kSmemPerCta2;
+        const double eff = (work / slots) * ((double)OH * OW / (work * RL * kStrip)) * (two ? 1.0 : 0.85);
+        cands[n++] = Cand{TH, TWc, rows, cols, smem, tiles_h, tiles_w, eff, (double)tiles_h * tiles_w * n_batch_ct, two};
+        if (eff > best_eff) best_eff = eff;
+    };
+    if (force_th && force_tw) {
+        consider(force_th, force_tw);
+    } else {
+        for (const TileShape& t : kTilePreference) consider(t.th, t.tw);
     }
-    return best > 0.0;
+    if (n == 0) return false;
+    int pick = -1, most = -1;
+    for (int i = 0; i < n; ++i) {
+        if (cands[i].eff < 0.97 * best_eff) continue;
+        if (most < 0 || cands[i].blocks > cands[most].blocks) most = i;
+        if (cands[i].blocks >= 3.0 * (cands[i].two ? 2 : 1) * sms) { pick = i; break; }
+    }
+    if (pick < 0) pick = most;
+    const Cand& c = cands[pick];
+    p->TH = c.th; p->TWc = c.tw; p->rows = c.rows; p->cols = c.cols;
+    p->tiles_h = c.tiles_h; p->tiles_w = c.tiles_w;
+    p->n_strips = c.tw / kStrip; p->n_items = (c.th / RL) * (c.tw / kStrip);
+    *smem_bytes = c.smem;
+    return true;
 }
 
 template <typename T, int K, int CT, int MATH>
@@ -211,7 +253,7 @@ int launch_tiled(const TiledArgs& a) {
     using wreg_t = typename WReg<T, MIXED>::type;
     TiledParams p{};
     p.w = a.w; p.bias = a.bias; p.out = a.out;
-    p.OH = a.OH; p.OW = a.OW; p.C = a.C;
+    p.H = a.H; p.W = a.W; p.OH = a.OH; p.OW = a.OW; p.C = a.C;
     p.KH = a.KH; p.pad_h = a.pad_h; p.pad_w = a.pad_w; p.flip = a.flip;
     p.nct = ceil_div(a.C, CT);
     p.status = a.status;
@@ -261,6 +303,7 @@ struct WgradParams {
     float* partial;      // [S][KH*K*C]
     float* partial_b;    // [S][C]
     int C, KH, pad_h, pad_w;
+    int OH, OW;          // grad_out extents
     int TH, TWc;
     int xrows, xcols, gcols;
     int tiles_w, tiles_h, n_tiles;   // n_tiles = B * tiles_h * tiles_w
@@ -277,8 +320,18 @@ struct WgradPlan {
     size_t workspace_bytes;
 };
 
+// Number of warps of the weight-gradient block.  For K = 9, 13, 17 (K-1 divisible by 4) the block has
+// K-1 warps - the same number on each of the SM's four schedulers - each owning one filter row; the
+// last filter row is shared: its tile rows are dealt out among all warps.  (With K warps one scheduler
+// would carry one warp more than the others and the rest would idle at every tile barrier.)  Other
+// widths use one warp per filter row.
+template <int K> struct WgradWarps {
+    static constexpr bool kShareLast = (K >= 9) && ((K - 1) % 4 == 0);
+    static constexpr int kWarps = kShareLast ? K - 1 : K;
+};
+
 template <typename T, int K, int CT, int MATH>
-__global__ void __launch_bounds__(K * 32, 1)
+__global__ void __launch_bounds__(WgradWarps<K>::kWarps * 32, 1)
 dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_g,
                     const WgradParams p) {
     using E = Elem<T>;
@@ -289,6 +342,8 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     constexpr int RL = 32 / CPL;
     constexpr int PIXB = CT * (int)sizeof(T);
     constexpr int MAX_STAGES = 4;
+    constexpr bool SHARE = WgradWarps<K>::kShareLast;
+    constexpr int NW = WgradWarps<K>::kWarps;
 
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // MAX_STAGES barriers in the first 128 bytes
@@ -297,7 +352,7 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
     const int ct = blockIdx.x % p.nct;
     const int s = blockIdx.x / p.nct;
-    const int kh = threadIdx.x >> 5;
+    const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int cp = lane % CPL, rl = lane / CPL;
 
@@ -325,13 +380,59 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     }
 
-    float2 acc[K];
+    float2 acc[K];                      // dW[warp, 0..K-1, pair]
+    float2 acc_last[SHARE ? K : 1];     // this warp's share of dW[K-1, 0..K-1, pair]
 #pragma unroll
     for (int kw = 0; kw < K; ++kw) acc[kw] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int kw = 0; kw < (SHARE ? K : 1); ++kw) acc_last[kw] = make_float2(0.f, 0.f);
     float2 bsum = make_float2(0.f, 0.f);
-    const bool bias_warp = p.want_bias && (kh == (p.KH > 1 ? 1 : 0));
+    const bool bias_warp = p.want_bias && (warp == (NW > 1 ? 1 : 0));
     const int xrow_bytes = p.xcols * PIXB, grow_bytes = p.gcols * PIXB;
-    const int n_chunks = p.TWc / kStrip;
+
+    // One tile row r against filter row kh: a[kw] += sum_w g[r, w] * x[r + kh, w + kw], in chunks of
+    // 16 columns; chunks that lie wholly right of the image (ragged last tile) are skipped.
+    auto row_times_filter_row = [&](float2* a, const unsigned char* xs, const unsigned char* gs, int r, int kh,
+                                    int n_chunks, bool add_bias) {
+        const unsigned char* gp = gs + (size_t)r * grow_bytes + cp * (int)sizeof(pair_t);
+        const unsigned char* xp = xs + (size_t)(r + kh) * xrow_bytes + cp * (int)sizeof(pair_t);
+        for (int ch = 0; ch < n_chunks; ++ch) {
+            greg_t g[kStrip];
+#pragma unroll
+            for (int o = 0; o < kStrip; ++o) {
+                const pair_t gv = *reinterpret_cast<const pair_t*>(gp + o * PIXB);
+                if constexpr (MIXED) g[o] = gv; else g[o] = E::unpack(gv);
+            }
+            if (add_bias) {
+#pragma unroll
+                for (int o = 0; o < kStrip; ++o) {
+                    float2 gf;
+                    if constexpr (MIXED) gf = E::unpack(g[o]); else gf = g[o];
+                    bsum.x += gf.x; bsum.y += gf.y;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kStrip + K - 1; ++j) {
+                const pair_t xv = *reinterpret_cast<const pair_t*>(xp + j * PIXB);
+                if constexpr (MIXED) {
+#pragma unroll
+                    for (int kw = 0; kw < K; ++kw) {
+                        const int o = j - kw;
+                        if (o >= 0 && o < kStrip) fma_mixed<T>(a[kw], g[o], xv);
+                    }
+                } else {
+                    const float2 xf = E::unpack(xv);
+#pragma unroll
+                    for (int kw = 0; kw < K; ++kw) {
+                        const int o = j - kw;
+                        if (o >= 0 && o < kStrip) ffma2(a[kw], g[o], xf);
+                    }
+                }
+            }
+            gp += kStrip * PIXB;
+            xp += kStrip * PIXB;
+        }
+    };
 
     int it = 0;
     for (int tile = s; tile < p.n_tiles; tile += p.S, ++it) {
@@ -342,44 +443,18 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
         const unsigned char* xs = stage0 + (size_t)st * stage_bytes;
         const unsigned char* gs = xs + p.x_stage_bytes;
-        for (int r = rl; r < p.TH; r += RL) {
-            const unsigned char* gp = gs + (size_t)r * grow_bytes + cp * (int)sizeof(pair_t);
-            const unsigned char* xp = xs + (size_t)(r + kh) * xrow_bytes + cp * (int)sizeof(pair_t);
-            for (int ch = 0; ch < n_chunks; ++ch) {
-                greg_t g[kStrip];
-#pragma unroll
-                for (int o = 0; o < kStrip; ++o) {
-                    const pair_t gv = *reinterpret_cast<const pair_t*>(gp + o * PIXB);
-                    if constexpr (MIXED) g[o] = gv; else g[o] = E::unpack(gv);
-                }
-                if (bias_warp) {
-#pragma unroll
-                    for (int o = 0; o < kStrip; ++o) {
-                        float2 gf;
-                        if constexpr (MIXED) gf = E::unpack(g[o]); else gf = g[o];
-                        bsum.x += gf.x; bsum.y += gf.y;
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kStrip + K - 1; ++j) {
-                    const pair_t xv = *reinterpret_cast<const pair_t*>(xp + j * PIXB);
-                    if constexpr (MIXED) {
-#pragma unroll
-                        for (int kw = 0; kw < K; ++kw) {
-                            const int o = j - kw;
-                            if (o >= 0 && o < kStrip) fma_mixed<T>(acc[kw], g[o], xv);
-                        }
-                    } else {
-                        const float2 xf = E::unpack(xv);
-#pragma unroll
-                        for (int kw = 0; kw < K; ++kw) {
-                            const int o = j - kw;
-                            if (o >= 0 && o < kStrip) ffma2(acc[kw], g[o], xf);
-                        }
-                    }
-                }
-                gp += kStrip * PIXB;
-                xp += kStrip * PIXB;
+        // Rows / column chunks of this tile that hold image pixels (the rest of a ragged tile is zeros).
+        const int tw = tile % p.tiles_w, th = (tile / p.tiles_w) % p.tiles_h;
+        const int rows_valid = min(p.TH, p.OH - th * p.TH);
+        const int n_chunks = min(p.TWc, p.OW - tw * p.TWc + kStrip - 1) / kStrip;
+        for (int r = rl; r < rows_valid; r += RL) row_times_filter_row(acc, xs, gs, r, warp, n_chunks, bias_warp);
+        if constexpr (SHARE) {
+            // Row groups of RL rows of the shared filter row, dealt round-robin; the starting warp
+            // rotates with the tile so that leftovers do not always land on the same warps.
+            const int groups = (rows_valid + RL - 1) / RL;
+            for (int grp = (warp + NW - (it % NW)) % NW; grp < groups; grp += NW) {
+                const int r = grp * RL + rl;
+                if (r < rows_valid) row_times_filter_row(acc_last, xs, gs, r, K - 1, n_chunks, false);
             }
         }
         __syncthreads();   // every warp is done with this stage: refill it
@@ -390,25 +465,44 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
 
     // Fold the row lanes (warp shuffles), then one fp32 store per (block, tap, channel pair).
-#pragma unroll
-    for (int kw = 0; kw < K; ++kw) {
+    auto fold = [&](float2& v) {
 #pragma unroll
         for (int off = CPL; off < 32; off <<= 1) {
-            acc[kw].x += __shfl_xor_sync(0xffffffffu, acc[kw].x, off);
-            acc[kw].y += __shfl_xor_sync(0xffffffffu, acc[kw].y, off);
+            v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+            v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
         }
-    }
+    };
 #pragma unroll
-    for (int off = CPL; off < 32; off <<= 1) {
-        bsum.x += __shfl_xor_sync(0xffffffffu, bsum.x, off);
-        bsum.y += __shfl_xor_sync(0xffffffffu, bsum.y, off);
-    }
+    for (int kw = 0; kw < K; ++kw) fold(acc[kw]);
+    fold(bsum);
     const int c = ct * CT + 2 * cp;
+    float* part = p.partial + (size_t)s * p.KH * K * p.C;
     if (rl == 0 && c < p.C) {
-        float* dst = p.partial + (size_t)s * p.KH * K * p.C + (size_t)kh * K * p.C + c;
+        float* dst = part + (size_t)warp * K * p.C + c;
 #pragma unroll
         for (int kw = 0; kw < K; ++kw) *reinterpret_cast<float2*>(dst + (size_t)kw * p.C) = acc[kw];
         if (bias_warp) *reinterpret_cast<float2*>(p.partial_b + (size_t)s * p.C + c) = bsum;
+    }
+    if constexpr (SHARE) {
+        // The shared filter row: block-level reduction over the warps through shared memory (all tile
+        // loads have completed and been consumed, the stage memory is free).
+        float2* red = reinterpret_cast<float2*>(stage0);     // [NW][K][CPL]
+#pragma unroll
+        for (int kw = 0; kw < K; ++kw) fold(acc_last[kw]);
+        if (rl == 0) {
+#pragma unroll
+            for (int kw = 0; kw < K; ++kw) red[(warp * K + kw) * CPL + cp] = acc_last[kw];
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < K * CPL; i += NW * 32) {
+            float2 sum = make_float2(0.f, 0.f);
+            for (int w = 0; w < NW; ++w) {
+                const float2 v = red[w * K * CPL + i];
+                sum.x += v.x; sum.y += v.y;
+            }
+            const int kw = i / CPL, cc = ct * CT + 2 * (i % CPL);
+            if (cc < p.C) *reinterpret_cast<float2*>(part + ((size_t)(K - 1) * K + kw) * p.C + cc) = sum;
+        }
     }
 }
 
@@ -429,47 +523,62 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, const flo
     }
 }
 
-template <int CT>
-inline bool plan_wgrad(int B, int OH, int OW, int C, int KH, int K, int esize, int sms, WgradPlan* plan) {
+// Tile for the weight-gradient kernel: the first shape of the preference list whose ring has at
+// least two stages and that wastes (almost) no row groups / column chunks at the image edges.
+template <int CT, int K_>
+inline bool plan_wgrad(int B, int OH, int OW, int C, int KH, int esize, int sms, WgradPlan* plan) {
+    constexpr int K = K_;
     constexpr int CPL = CT / 2, RL = 32 / CPL;
     const int pixb = CT * esize;
     WgradParams& p = plan->p;
     p.nct = ceil_div(C, CT);
-    double best = -1.0;
-    for (int TH = RL; TH <= 64; TH += RL) {
-        for (int TWc = kStrip; TWc <= 128; TWc += kStrip) {
-            const int xrows = TH + KH - 1;
-            int xcols = TWc + K - 1, gcols = TWc;
-            if (RL > 1 && (xcols % 2) == 0) xcols++;
-            if (RL > 1 && (gcols % 2) == 0) gcols++;
-            if (xrows > 256 || xcols > 256) continue;
-            const int xb = round_up(xrows * xcols * pixb, 128), gb = round_up(TH * gcols * pixb, 128);
-            int NS = (kSmemMax - 128) / (xb + gb);
-            if (NS < 2) continue;
-            if (NS > 3) NS = 3;
-            const int tiles_h = ceil_div(OH, TH), tiles_w = ceil_div(OW, TWc);
-            const long long n_tiles = (long long)B * tiles_h * tiles_w;
-            if (n_tiles > 0x7fffffffLL) continue;
-            int S = sms / p.nct;
-            if (S < 1) S = 1;
-            if (S > n_tiles) S = (int)n_tiles;
-            const double eff_sp = (double)OH * OW / ((double)tiles_h * TH * tiles_w * TWc);
-            const double per = (double)n_tiles / S;
-            const double eff_bal = per / (double)(long long)(per + 0.999999);
-            const double halo = (double)TH * TWc / ((double)xrows * xcols);
-            const double score = eff_sp * eff_bal * (0.9 + 0.1 * halo) * (NS >= 3 ? 1.0 : 0.97);
-            if (score > best) {
-                best = score;
-                p.TH = TH; p.TWc = TWc; p.xrows = xrows; p.xcols = xcols; p.gcols = gcols;
-                p.tiles_h = tiles_h; p.tiles_w = tiles_w; p.n_tiles = (int)n_tiles;
-                p.S = S; p.NS = NS; p.x_stage_bytes = xb; p.g_stage_bytes = gb;
-                plan->smem_bytes = 128 + NS * (xb + gb);
-            }
-        }
+    const int force_th = tuning(5), force_tw = tuning(6);
+    struct Cand { int th, tw, xrows, xcols, gcols, xb, gb, ns; double eff; };
+    Cand cands[16];
+    int n = 0;
+    double best_eff = 0.0;
+    auto consider = [&](int TH, int TWc) {
+        if (TH % RL != 0 || TWc % kStrip != 0) return;
+        const int xrows = TH + KH - 1;
+        int xcols = TWc + K - 1, gcols = TWc;
+        if (RL > 1 && (xcols % 2) == 0) xcols++;
+        if (RL > 1 && (gcols % 2) == 0) gcols++;
+        if (xrows > 256 || xcols > 256) return;
+        const int xb = round_up(xrows * xcols * pixb, 128), gb = round_up(TH * gcols * pixb, 128);
+        int NS = (kSmemMax - 128) / (xb + gb);
+        if (NS < 2) return;
+        if (NS > 3) NS = 3;
+        if ((long long)B * ceil_div(OH, TH) * ceil_div(OW, TWc) > 0x7fffffffLL) return;
+        // Rows and 16-column chunks beyond the image are skipped by the kernel, so edge waste only
+        // counts at the granularity of a row group / chunk.
+        const int row_units = (OH / TH) * TH + round_up(OH % TH, RL);
+        const int col_units = (OW / TWc) * TWc + round_up(OW % TWc, kStrip);
+        const double eff = (double)OH * OW / ((double)row_units * col_units);
+        cands[n++] = Cand{TH, TWc, xrows, xcols, gcols, xb, gb, NS, eff};
+        if (eff > best_eff) best_eff = eff;
+    };
+    if (force_th && force_tw) {
+        consider(force_th, force_tw);
+    } else {
+        for (const TileShape& t : kTilePreference) consider(t.th, t.tw);
     }
-    if (best <= 0.0) return false;
-    p.C = C; p.KH = KH;
-    plan->threads = KH * 32;
+    int pick = -1;
+    for (int i = 0; i < n && pick < 0; ++i) {
+        if (cands[i].eff >= 0.97 * best_eff) pick = i;
+    }
+    if (pick < 0) return false;
+    const Cand& c = cands[pick];
+    const int tiles_h = ceil_div(OH, c.th), tiles_w = ceil_div(OW, c.tw);
+    const long long n_tiles = (long long)B * tiles_h * tiles_w;
+    int S = sms / p.nct;
+    if (S < 1) S = 1;
+    if (S > n_tiles) S = (int)n_tiles;
+    p.TH = c.th; p.TWc = c.tw; p.xrows = c.xrows; p.xcols = c.xcols; p.gcols = c.gcols;
+    p.tiles_h = tiles_h; p.tiles_w = tiles_w; p.n_tiles = (int)n_tiles;
+    p.S = S; p.NS = c.ns; p.x_stage_bytes = c.xb; p.g_stage_bytes = c.gb;
+    plan->smem_bytes = 128 + c.ns * (c.xb + c.gb);
+    p.C = C; p.KH = KH; p.OH = OH; p.OW = OW;
+    plan->threads = WgradWarps<K_>::kWarps * 32;
     plan->workspace_bytes = (size_t)p.S * ((size_t)KH * K * C + C) * sizeof(float);
     return true;
 }
@@ -477,7 +586,7 @@ inline bool plan_wgrad(int B, int OH, int OW, int C, int KH, int K, int esize, i
 template <typename T, int K, int CT, int MATH>
 int launch_wgrad(const WgradArgs& a) {
     WgradPlan plan{};
-    if (a.KH != K || !plan_wgrad<CT>(a.B, a.OH, a.OW, a.C, a.KH, K, (int)sizeof(T), sm_count(), &plan))
+    if (a.KH != K || !plan_wgrad<CT, K>(a.B, a.OH, a.OW, a.C, a.KH, (int)sizeof(T), sm_count(), &plan))
         return PDW_ERR_UNSUPPORTED;
     if (a.workspace == nullptr || a.workspace_bytes < plan.workspace_bytes) return PDW_ERR_WORKSPACE;
     WgradParams& p = plan.p;

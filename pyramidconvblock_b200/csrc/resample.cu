@@ -29,60 +29,64 @@ __device__ __forceinline__ int win_end(int o, int in, int out) {
     return (int)((((long long)o + 1) * in + out - 1) / out);
 }
 
-struct Shape { int B, H, W, C, OH, OW; };   // H,W: larger-index "input" of the forward op
+struct Shape { int B, H, W, C, OH, OW; };   // forward op: [H,W] -> [OH,OW]
+
+constexpr int kRowThreads = 256;
+
+// Every spatial kernel below runs one thread block per written row (b, row): what depends on the row
+// alone is computed once, the threads then sweep the row's (column, 16-byte channel vector) pairs with
+// the vector index fastest, so a warp touches consecutive 16-byte pieces of consecutive pixels, and all
+// index arithmetic is 32-bit.
 
 // ---- adaptive average pool ------------------------------------------------------------------
 template <typename T, int V>
-__global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s, const long long total) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int cv = s.C / V;
-    const int c = (int)(idx % cv) * V;
-    long long t = idx / cv;
-    const int ow = (int)(t % s.OW);  t /= s.OW;
-    const int oh = (int)(t % s.OH);
-    const int b = (int)(t / s.OH);
+__global__ void __launch_bounds__(kRowThreads) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s) {
+    const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
+    const int cv = s.C / V, n = s.OW * cv;
     const int hs = win_start(oh, s.H, s.OH), he = win_end(oh, s.H, s.OH);
-    const int ws = win_start(ow, s.W, s.OW), we = win_end(ow, s.W, s.OW);
-    float acc[V];
+    const T* xin = x + ((size_t)b * s.H + hs) * s.W * s.C;
+    T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.C;
+    const size_t row_stride = (size_t)s.W * s.C;
+    for (int t = threadIdx.x; t < n; t += kRowThreads) {
+        const int ow = t / cv, c = (t - ow * cv) * V;
+        const int ws = win_start(ow, s.W, s.OW), we = win_end(ow, s.W, s.OW);
+        float acc[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    for (int ih = hs; ih < he; ++ih) {
-        const T* row = x + (((size_t)b * s.H + ih) * s.W) * s.C + c;
-        for (int iw = ws; iw < we; ++iw) load_acc<T, V>(row + (size_t)iw * s.C, acc, 1.f);
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        const T* p = xin + (size_t)ws * s.C + c;
+        for (int ih = hs; ih < he; ++ih, p += row_stride)
+            for (int iw = 0; iw < we - ws; ++iw) load_acc<T, V>(p + (size_t)iw * s.C, acc, 1.f);
+        const float inv = 1.f / (float)((he - hs) * (we - ws));
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] *= inv;
+        store_vec<T, V>(yrow + (size_t)ow * s.C + c, acc);
     }
-    const float inv = 1.f / (float)((he - hs) * (we - ws));
-#pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] *= inv;
-    store_vec<T, V>(y + (size_t)idx * V, acc);
 }
 
 // dx[ih,iw] = sum over the outputs whose window holds (ih,iw) of grad_out / window area.  The
 // outputs that hold input index i are exactly [floor(i*out/in), ceil((i+1)*out/in)).
 template <typename T, int V>
-__global__ void pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s, const long long total) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int cv = s.C / V;
-    const int c = (int)(idx % cv) * V;
-    long long t = idx / cv;
-    const int iw = (int)(t % s.W);  t /= s.W;
-    const int ih = (int)(t % s.H);
-    const int b = (int)(t / s.H);
+__global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s) {
+    const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
+    const int cv = s.C / V, n = s.W * cv;
     const int oh0 = win_start(ih, s.OH, s.H), oh1 = win_end(ih, s.OH, s.H);
-    const int ow0 = win_start(iw, s.OW, s.W), ow1 = win_end(iw, s.OW, s.W);
-    float acc[V];
+    T* drow = dx + ((size_t)b * s.H + ih) * s.W * s.C;
+    for (int t = threadIdx.x; t < n; t += kRowThreads) {
+        const int iw = t / cv, c = (t - iw * cv) * V;
+        const int ow0 = win_start(iw, s.OW, s.W), ow1 = win_end(iw, s.OW, s.W);
+        float acc[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    for (int oh = oh0; oh < oh1; ++oh) {
-        const int kh = win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH);
-        const T* row = go + (((size_t)b * s.OH + oh) * s.OW) * s.C + c;
-        for (int ow = ow0; ow < ow1; ++ow) {
-            const int kw = win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW);
-            load_acc<T, V>(row + (size_t)ow * s.C, acc, 1.f / (float)(kh * kw));
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int oh = oh0; oh < oh1; ++oh) {
+            const int kh = win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH);
+            const T* row = go + (((size_t)b * s.OH + oh) * s.OW) * s.C + c;
+            for (int ow = ow0; ow < ow1; ++ow) {
+                const int kw = win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW);
+                load_acc<T, V>(row + (size_t)ow * s.C, acc, 1.f / (float)(kh * kw));
+            }
         }
+        store_vec<T, V>(drow + (size_t)iw * s.C + c, acc);
     }
-    store_vec<T, V>(dx + (size_t)idx * V, acc);
 }
 
 // ---- bilinear resize (align_corners = False) ---------------------------------------------------
@@ -102,27 +106,26 @@ __device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
 
 // s.H,s.W: source extent (small), s.OH,s.OW: destination extent.
 template <typename T, int V>
-__global__ void upsample_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s, float scale_h,
-                                    float scale_w, const long long total) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int cv = s.C / V;
-    const int c = (int)(idx % cv) * V;
-    long long t = idx / cv;
-    const int ow = (int)(t % s.OW);  t /= s.OW;
-    const int oh = (int)(t % s.OH);
-    const int b = (int)(t / s.OH);
-    const Tap ty = source_taps(oh, scale_h, s.H), tx = source_taps(ow, scale_w, s.W);
-    const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C + c;
-    const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C + c;
-    float acc[V];
+__global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s,
+                                                                   float scale_h, float scale_w) {
+    const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
+    const int cv = s.C / V, n = s.OW * cv;
+    const Tap ty = source_taps(oh, scale_h, s.H);
+    const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C;
+    const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C;
+    T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.C;
+    for (int t = threadIdx.x; t < n; t += kRowThreads) {
+        const int ow = t / cv, c = (t - ow * cv) * V;
+        const Tap tx = source_taps(ow, scale_w, s.W);
+        float acc[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    load_acc<T, V>(r0 + (size_t)tx.i0 * s.C, acc, ty.l0 * tx.l0);
-    load_acc<T, V>(r0 + (size_t)tx.i1 * s.C, acc, ty.l0 * tx.l1);
-    load_acc<T, V>(r1 + (size_t)tx.i0 * s.C, acc, ty.l1 * tx.l0);
-    load_acc<T, V>(r1 + (size_t)tx.i1 * s.C, acc, ty.l1 * tx.l1);
-    store_vec<T, V>(y + (size_t)idx * V, acc);
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        load_acc<T, V>(r0 + (size_t)tx.i0 * s.C + c, acc, ty.l0 * tx.l0);
+        load_acc<T, V>(r0 + (size_t)tx.i1 * s.C + c, acc, ty.l0 * tx.l1);
+        load_acc<T, V>(r1 + (size_t)tx.i0 * s.C + c, acc, ty.l1 * tx.l0);
+        load_acc<T, V>(r1 + (size_t)tx.i1 * s.C + c, acc, ty.l1 * tx.l1);
+        store_vec<T, V>(yrow + (size_t)ow * s.C + c, acc);
+    }
 }
 
 // Weight with which destination index `dst` reads source index `i` (0 if it does not).
@@ -140,9 +143,63 @@ __device__ __forceinline__ void dst_range(int i, float scale, int out, int* lo, 
     *hi = b > out - 1 ? out - 1 : b;
 }
 
+// Adjoint of the resize as a gather.  Per block (one source row iy): the destination rows that read
+// iy and their weights go to shared memory once, and so does, for every source column, the span of
+// destination columns reading it with their weights (kMaxTaps per index; the host checks that this
+// suffices, else upsample_bwd_direct_kernel runs).  The sweep over the row is then loads and FMAs only.
+constexpr int kMaxTaps = 24;
 template <typename T, int V>
-__global__ void upsample_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s, float scale_h,
-                                    float scale_w, const long long total) {
+__global__ void __launch_bounds__(kRowThreads) upsample_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
+                                                                   float scale_h, float scale_w) {
+    extern __shared__ float tab[];
+    float* wy = tab;                                   // [kMaxTaps]
+    int* meta = reinterpret_cast<int*>(tab + kMaxTaps);  // [2 + 2*W]: oy0, ny, then (ox0, nx) per column
+    float* wx = tab + kMaxTaps + 2 + 2 * s.W;          // [W][kMaxTaps]
+    const int iy = blockIdx.x % s.H, b = blockIdx.x / s.H;
+    if (threadIdx.x == 0) {
+        int lo, hi;
+        dst_range(iy, scale_h, s.OH, &lo, &hi);
+        while (lo <= hi && tap_weight(lo, iy, scale_h, s.H) == 0.f) ++lo;
+        while (hi >= lo && tap_weight(hi, iy, scale_h, s.H) == 0.f) --hi;
+        meta[0] = lo;
+        meta[1] = hi - lo + 1;
+        for (int j = 0; j <= hi - lo && j < kMaxTaps; ++j) wy[j] = tap_weight(lo + j, iy, scale_h, s.H);
+    }
+    for (int ix = threadIdx.x; ix < s.W; ix += kRowThreads) {
+        int lo, hi;
+        dst_range(ix, scale_w, s.OW, &lo, &hi);
+        while (lo <= hi && tap_weight(lo, ix, scale_w, s.W) == 0.f) ++lo;
+        while (hi >= lo && tap_weight(hi, ix, scale_w, s.W) == 0.f) --hi;
+        meta[2 + 2 * ix] = lo;
+        meta[3 + 2 * ix] = hi - lo + 1;
+        for (int j = 0; j <= hi - lo && j < kMaxTaps; ++j) wx[ix * kMaxTaps + j] = tap_weight(lo + j, ix, scale_w, s.W);
+    }
+    __syncthreads();
+    const int oy0 = meta[0], ny = meta[1];
+    const int cv = s.C / V, n = s.W * cv;
+    const T* gbase = go + ((size_t)b * s.OH + oy0) * s.OW * s.C;
+    const size_t row_stride = (size_t)s.OW * s.C;
+    T* drow = dx + ((size_t)b * s.H + iy) * s.W * s.C;
+    for (int t = threadIdx.x; t < n; t += kRowThreads) {
+        const int ix = t / cv, c = (t - ix * cv) * V;
+        const int ox0 = meta[2 + 2 * ix], nx = meta[3 + 2 * ix];
+        const float* wxi = wx + ix * kMaxTaps;
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        const T* p = gbase + (size_t)ox0 * s.C + c;
+        for (int jy = 0; jy < ny; ++jy, p += row_stride) {
+            const float wyj = wy[jy];
+            for (int jx = 0; jx < nx; ++jx) load_acc<T, V>(p + (size_t)jx * s.C, acc, wyj * wxi[jx]);
+        }
+        store_vec<T, V>(drow + (size_t)ix * s.C + c, acc);
+    }
+}
+
+// Same adjoint without tables, for extents the tables do not cover (very large ratios or widths).
+template <typename T, int V>
+__global__ void upsample_bwd_direct_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s, float scale_h,
+                                           float scale_w, const long long total) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int cv = s.C / V;
@@ -244,6 +301,12 @@ enum class Resample { PoolFwd, PoolBwd, UpFwd, UpBwd };
 
 // Shared argument checking + launch of the four spatial resampling kernels.  `src`/`dst` are the
 // tensors read and written; (H,W) is the forward op's input extent, (OH,OW) its output extent.
+// Largest number of destination indices that read one source index, for a resize in -> out.
+static int max_taps_per_source(int in, int out) {
+    if (out <= in) return 4;
+    return 2 * ((out + in - 1) / in) + 4;
+}
+
 template <Resample OP>
 static int run_resample(const void* src, void* dst, int B, int H, int W, int C, int OH, int OW, int dtype,
                         void* stream) {
@@ -255,11 +318,11 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
     const int v = vec_width(dtype, C, src, dst);
     constexpr bool writes_small = (OP == Resample::PoolFwd || OP == Resample::UpBwd);
     constexpr bool pool = (OP == Resample::PoolFwd || OP == Resample::PoolBwd);
-    // Pool: (H,W) is the big side.  Upsample: (H,W) is the small side.  One thread per written vector.
+    // Pool: (H,W) is the big side.  Upsample: (H,W) is the small side.  One block per written row.
     const bool dst_is_hw = pool ? !writes_small : writes_small;
-    const long long total = (long long)B * (dst_is_hw ? (long long)H * W : (long long)OH * OW) * (C / v);
-    unsigned blocks;
-    if (!grid_for(total, &blocks)) return PDW_ERR_BAD_SHAPE;
+    const long long rows = (long long)B * (dst_is_hw ? H : OH);
+    if (rows > 0x7fffffffLL || (long long)(dst_is_hw ? W : OW) * C > 0x7fffffffLL) return PDW_ERR_BAD_SHAPE;
+    const unsigned blocks = (unsigned)rows;
     const Shape s{B, H, W, C, OH, OW};
     const float sh = (float)H / (float)OH, sw = (float)W / (float)OW;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -268,10 +331,20 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
         constexpr int V = decltype(w)::value;
         const T* in = static_cast<const T*>(src);
         T* out = static_cast<T*>(dst);
-        if constexpr (OP == Resample::PoolFwd) pool_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, total);
-        else if constexpr (OP == Resample::PoolBwd) pool_bwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, total);
-        else if constexpr (OP == Resample::UpFwd) upsample_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, sh, sw, total);
-        else upsample_bwd_kernel<T, V><<<blocks, 256, 0, st>>>(in, out, s, sh, sw, total);
+        if constexpr (OP == Resample::PoolFwd) pool_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+        else if constexpr (OP == Resample::PoolBwd) pool_bwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+        else if constexpr (OP == Resample::UpFwd) upsample_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
+        else {
+            const size_t table = sizeof(float) * (kMaxTaps + 2 + 2 * (size_t)W + (size_t)W * kMaxTaps);
+            if (max_taps_per_source(H, OH) <= kMaxTaps && max_taps_per_source(W, OW) <= kMaxTaps && table <= 40 * 1024) {
+                upsample_bwd_kernel<T, V><<<blocks, kRowThreads, table, st>>>(in, out, s, sh, sw);
+            } else {
+                const long long total = (long long)B * H * W * (C / V);
+                unsigned nb;
+                if (!grid_for(total, &nb)) return (int)PDW_ERR_BAD_SHAPE;
+                upsample_bwd_direct_kernel<T, V><<<nb, 256, 0, st>>>(in, out, s, sh, sw, total);
+            }
+        }
         return check_launch();
     });
 }
