@@ -169,6 +169,34 @@ int pdw_gate_bwd(const void* conv_out, const void* grad_y, void* grad_conv_out, 
                  int channels, float inv_scale, int dtype, void* stream);
 
 /*
+ * Variants for ConvBlock's concatenation (pyramid_dwconv/conv_block.py:43, torch.cat of the branch
+ * outputs): a branch writes its result straight into its channel slice of the concatenated buffer
+ * and, in backward, reads its slice of the concatenated gradient in place, so neither the cat kernel
+ * nor strided copies of the slices are needed.  `ld_*` is the pixel stride in elements of that one
+ * sliced tensor (the width of the concatenated buffer); the pointer is the slice's first element.
+ */
+int pdw_gate_fwd_strided(const void* conv_out, void* y, int64_t pixels, int channels, int ld_y,
+                         float inv_scale, int dtype, void* stream);
+int pdw_gate_bwd_strided(const void* conv_out, const void* grad_y, void* grad_conv_out, int64_t pixels,
+                         int channels, int ld_grad_y, float inv_scale, int dtype, void* stream);
+int pdw_upsample_fwd_strided(const void* x, void* y, int batch, int in_h, int in_w, int channels,
+                             int out_h, int out_w, int ld_y, int dtype, void* stream);
+int pdw_upsample_bwd_strided(const void* grad_out, void* dx, int batch, int in_h, int in_w, int channels,
+                             int out_h, int out_w, int ld_grad_out, int dtype, void* stream);
+/* pdw_pool_bwd that adds into dx instead of overwriting it: the pooled branch's input gradient is
+ * accumulated onto the full-resolution branch's (both are gradients of the same conv_up output,
+ * conv_block.py:40-41), saving autograd's separate add. */
+int pdw_pool_bwd_accumulate(const void* grad_out, void* dx, int batch, int in_h, int in_w, int channels,
+                            int out_h, int out_w, int dtype, void* stream);
+/*
+ * y[b, i, :] += alpha * v[b, :] for all pixels i of image b, in place; y is [B, pixels, C], v is [B, C].
+ * Forward: the broadcast "+ x_pool" of conv_block.py:49.  Backward: the gradient of the spatial mean
+ * (conv_block.py:46) added onto dX with alpha = 1/(H*W).
+ */
+int pdw_add_pooled(void* y, const void* v, int batch, int64_t pixels_per_image, int channels, float alpha,
+                   int dtype, void* stream);
+
+/*
  * Experiment hook, not part of the reference surface: selects between equivalent inner-loop
  * code paths of the tiled convolution kernels (key 0: arithmetic form for 16-bit inputs,
  * 0 = packed-pair FP32 FMA after conversion, 1 = mixed-precision FMA on the 16-bit operands;

@@ -19,6 +19,8 @@ EXPORTED_SYMBOLS = (
     "pdw_dwconv_fwd", "pdw_dwconv_bwd_input", "pdw_dwconv_bwd_weight_workspace", "pdw_dwconv_bwd_weight",
     "pdw_pool_fwd", "pdw_pool_bwd", "pdw_upsample_fwd", "pdw_upsample_bwd",
     "pdw_gate_fwd", "pdw_gate_bwd", "pdw_set_tuning", "pdw_dwconv_bwd_weight_static",
+    "pdw_gate_fwd_strided", "pdw_gate_bwd_strided", "pdw_upsample_fwd_strided", "pdw_upsample_bwd_strided",
+    "pdw_pool_bwd_accumulate", "pdw_add_pooled",
 )
 
 
@@ -60,6 +62,18 @@ def _declare(lib):
     lib.pdw_gate_fwd.argtypes = [vp, vp, i64, i32, f32, i32, vp]
     lib.pdw_gate_bwd.restype = i32
     lib.pdw_gate_bwd.argtypes = [vp, vp, vp, i64, i32, f32, i32, vp]
+    lib.pdw_gate_fwd_strided.restype = i32
+    lib.pdw_gate_fwd_strided.argtypes = [vp, vp, i64, i32, i32, f32, i32, vp]
+    lib.pdw_gate_bwd_strided.restype = i32
+    lib.pdw_gate_bwd_strided.argtypes = [vp, vp, vp, i64, i32, i32, f32, i32, vp]
+    for name in ("pdw_upsample_fwd_strided", "pdw_upsample_bwd_strided"):
+        fn = getattr(lib, name)
+        fn.restype = i32
+        fn.argtypes = [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.pdw_pool_bwd_accumulate.restype = i32
+    lib.pdw_pool_bwd_accumulate.argtypes = [vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.pdw_add_pooled.restype = i32
+    lib.pdw_add_pooled.argtypes = [vp, vp, i32, i64, i32, f32, i32, vp]
     lib.pdw_set_tuning.restype = i32
     lib.pdw_set_tuning.argtypes = [i32, i32]
     lib.pdw_dwconv_bwd_weight_static.restype = i32

@@ -24,12 +24,14 @@ __device__ __forceinline__ void store_vec(T* p, const float (&acc)[V]) {
     *reinterpret_cast<Vec<T, V>*>(p) = d;
 }
 
-__device__ __forceinline__ int win_start(int o, int in, int out) { return (int)(((long long)o * in) / out); }
-__device__ __forceinline__ int win_end(int o, int in, int out) {
-    return (int)((((long long)o + 1) * in + out - 1) / out);
-}
+// Window of adaptive pooling in exact integer arithmetic; the host checks that (o+1)*in + out fits
+// in 32 bits (extents up to 32767), so no 64-bit division is needed here.
+__device__ __forceinline__ int win_start(int o, int in, int out) { return (o * in) / out; }
+__device__ __forceinline__ int win_end(int o, int in, int out) { return ((o + 1) * in + out - 1) / out; }
 
-struct Shape { int B, H, W, C, OH, OW; };   // forward op: [H,W] -> [OH,OW]
+// Forward op: [H,W] -> [OH,OW].  `ld` is the pixel stride (in elements) of the one tensor of a call
+// that may be a channel slice of a wider NHWC buffer (the upsample output / its gradient); C if dense.
+struct Shape { int B, H, W, C, OH, OW, ld; };
 
 constexpr int kRowThreads = 256;
 
@@ -66,7 +68,8 @@ __global__ void __launch_bounds__(kRowThreads) pool_fwd_kernel(const T* __restri
 // dx[ih,iw] = sum over the outputs whose window holds (ih,iw) of grad_out / window area.  The
 // outputs that hold input index i are exactly [floor(i*out/in), ceil((i+1)*out/in)).
 template <typename T, int V>
-__global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s) {
+__global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
+                                                               const bool accumulate) {
     const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
     const int cv = s.C / V, n = s.W * cv;
     const int oh0 = win_start(ih, s.OH, s.H), oh1 = win_end(ih, s.OH, s.H);
@@ -85,6 +88,7 @@ __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restri
                 load_acc<T, V>(row + (size_t)ow * s.C, acc, 1.f / (float)(kh * kw));
             }
         }
+        if (accumulate) load_acc<T, V>(drow + (size_t)iw * s.C + c, acc, 1.f);   // dx += ...
         store_vec<T, V>(drow + (size_t)iw * s.C + c, acc);
     }
 }
@@ -113,7 +117,7 @@ __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __re
     const Tap ty = source_taps(oh, scale_h, s.H);
     const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C;
     const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C;
-    T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.C;
+    T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.ld;
     for (int t = threadIdx.x; t < n; t += kRowThreads) {
         const int ow = t / cv, c = (t - ow * cv) * V;
         const Tap tx = source_taps(ow, scale_w, s.W);
@@ -124,7 +128,7 @@ __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __re
         load_acc<T, V>(r0 + (size_t)tx.i1 * s.C + c, acc, ty.l0 * tx.l1);
         load_acc<T, V>(r1 + (size_t)tx.i0 * s.C + c, acc, ty.l1 * tx.l0);
         load_acc<T, V>(r1 + (size_t)tx.i1 * s.C + c, acc, ty.l1 * tx.l1);
-        store_vec<T, V>(yrow + (size_t)ow * s.C + c, acc);
+        store_vec<T, V>(yrow + (size_t)ow * s.ld + c, acc);
     }
 }
 
@@ -177,8 +181,8 @@ __global__ void __launch_bounds__(kRowThreads) upsample_bwd_kernel(const T* __re
     __syncthreads();
     const int oy0 = meta[0], ny = meta[1];
     const int cv = s.C / V, n = s.W * cv;
-    const T* gbase = go + ((size_t)b * s.OH + oy0) * s.OW * s.C;
-    const size_t row_stride = (size_t)s.OW * s.C;
+    const T* gbase = go + ((size_t)b * s.OH + oy0) * s.OW * s.ld;
+    const size_t row_stride = (size_t)s.OW * s.ld;
     T* drow = dx + ((size_t)b * s.H + iy) * s.W * s.C;
     for (int t = threadIdx.x; t < n; t += kRowThreads) {
         const int ix = t / cv, c = (t - ix * cv) * V;
@@ -187,10 +191,10 @@ __global__ void __launch_bounds__(kRowThreads) upsample_bwd_kernel(const T* __re
         float acc[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
-        const T* p = gbase + (size_t)ox0 * s.C + c;
+        const T* p = gbase + (size_t)ox0 * s.ld + c;
         for (int jy = 0; jy < ny; ++jy, p += row_stride) {
             const float wyj = wy[jy];
-            for (int jx = 0; jx < nx; ++jx) load_acc<T, V>(p + (size_t)jx * s.C, acc, wyj * wxi[jx]);
+            for (int jx = 0; jx < nx; ++jx) load_acc<T, V>(p + (size_t)jx * s.ld, acc, wyj * wxi[jx]);
         }
         store_vec<T, V>(drow + (size_t)ix * s.C + c, acc);
     }
@@ -217,11 +221,11 @@ __global__ void upsample_bwd_direct_kernel(const T* __restrict__ go, T* __restri
     for (int oy = oy0; oy <= oy1; ++oy) {
         const float wy = tap_weight(oy, iy, scale_h, s.H);
         if (wy == 0.f) continue;
-        const T* row = go + (((size_t)b * s.OH + oy) * s.OW) * s.C + c;
+        const T* row = go + (((size_t)b * s.OH + oy) * s.OW) * s.ld + c;
         for (int ox = ox0; ox <= ox1; ++ox) {
             const float wx = tap_weight(ox, ix, scale_w, s.W);
             if (wx == 0.f) continue;
-            load_acc<T, V>(row + (size_t)ox * s.C, acc, wy * wx);
+            load_acc<T, V>(row + (size_t)ox * s.ld, acc, wy * wx);
         }
     }
     store_vec<T, V>(dx + (size_t)idx * V, acc);
@@ -229,7 +233,7 @@ __global__ void upsample_bwd_direct_kernel(const T* __restrict__ go, T* __restri
 
 // ---- gate ----------------------------------------------------------------------------------------
 template <typename T, int V>
-__global__ void gate_fwd_kernel(const T* __restrict__ a, T* __restrict__ y, int C, float inv_scale,
+__global__ void gate_fwd_kernel(const T* __restrict__ a, T* __restrict__ y, int C, int ld_y, float inv_scale,
                                 const long long total) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -241,12 +245,12 @@ __global__ void gate_fwd_kernel(const T* __restrict__ a, T* __restrict__ y, int 
     float r[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) r[i] = Elem<T>::to_f(x1.v[i]) * (Elem<T>::to_f(x2.v[i]) * inv_scale);
-    store_vec<T, V>(y + (size_t)n * (C / 2) + j, r);
+    store_vec<T, V>(y + (size_t)n * ld_y + j, r);
 }
 
 template <typename T, int V>
 __global__ void gate_bwd_kernel(const T* __restrict__ a, const T* __restrict__ gy, T* __restrict__ ga, int C,
-                                float inv_scale, const long long total) {
+                                int ld_gy, float inv_scale, const long long total) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int hv = (C / 2) / V;
@@ -254,7 +258,7 @@ __global__ void gate_bwd_kernel(const T* __restrict__ a, const T* __restrict__ g
     const long long n = idx / hv;
     const Vec<T, V> x1 = *reinterpret_cast<const Vec<T, V>*>(a + (size_t)n * C + j);
     const Vec<T, V> x2 = *reinterpret_cast<const Vec<T, V>*>(a + (size_t)n * C + C / 2 + j);
-    const Vec<T, V> g = *reinterpret_cast<const Vec<T, V>*>(gy + (size_t)n * (C / 2) + j);
+    const Vec<T, V> g = *reinterpret_cast<const Vec<T, V>*>(gy + (size_t)n * ld_gy + j);
     float r1[V], r2[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) {
@@ -266,9 +270,34 @@ __global__ void gate_bwd_kernel(const T* __restrict__ a, const T* __restrict__ g
     store_vec<T, V>(ga + (size_t)n * C + C / 2 + j, r2);
 }
 
+// ---- broadcast add of a per-image row ----------------------------------------------------------------
+// y[b, i, :] += alpha * v[b, :] for every pixel i of image b: the "+ x_pool" of ConvBlock.forward
+// (pyramid_dwconv/conv_block.py:49) and, in backward, the gradient of the spatial mean, both in place.
+template <typename T, int V>
+__global__ void __launch_bounds__(kRowThreads) add_pooled_kernel(T* __restrict__ y, const T* __restrict__ v, int pixels_per_image,
+                                                                 int C, float alpha, int pixels_per_block) {
+    const int b = blockIdx.y;
+    const int cv = C / V;
+    const int p0 = blockIdx.x * pixels_per_block;
+    const int np = min(pixels_per_block, pixels_per_image - p0);
+    const int n = np * cv;
+    T* base = y + ((size_t)b * pixels_per_image + p0) * C;
+    const T* vb = v + (size_t)b * C;
+    for (int t = threadIdx.x; t < n; t += kRowThreads) {
+        const int c = (t % cv) * V;
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        load_acc<T, V>(vb + c, acc, alpha);
+        load_acc<T, V>(base + (size_t)t * V, acc, 1.f);
+        store_vec<T, V>(base + (size_t)t * V, acc);
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 static int check_shape(int B, int H, int W, int C, int OH, int OW) {
     if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || OH <= 0 || OW <= 0) return PDW_ERR_BAD_SHAPE;
+    if (H > 32767 || W > 32767 || OH > 32767 || OW > 32767) return PDW_ERR_BAD_SHAPE;   // 32-bit window arithmetic
     return PDW_OK;
 }
 // 16-byte vectors when the channel run and every base address allow it, else single elements.
@@ -309,13 +338,15 @@ static int max_taps_per_source(int in, int out) {
 
 template <Resample OP>
 static int run_resample(const void* src, void* dst, int B, int H, int W, int C, int OH, int OW, int dtype,
-                        void* stream) {
+                        void* stream, int ld = 0, bool accumulate = false) {
     if (!src || !dst) return PDW_ERR_NULL_POINTER;
     if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
     const int rc = check_shape(B, H, W, C, OH, OW);
     if (rc) return rc;
     if (!aligned_to(src, dtype_size(dtype)) || !aligned_to(dst, dtype_size(dtype))) return PDW_ERR_MISALIGNED;
-    const int v = vec_width(dtype, C, src, dst);
+    if (ld == 0) ld = C;
+    if (ld < C) return PDW_ERR_BAD_SHAPE;
+    const int v = (ld % (16 / (int)dtype_size(dtype)) == 0) ? vec_width(dtype, C, src, dst) : 1;
     constexpr bool writes_small = (OP == Resample::PoolFwd || OP == Resample::UpBwd);
     constexpr bool pool = (OP == Resample::PoolFwd || OP == Resample::PoolBwd);
     // Pool: (H,W) is the big side.  Upsample: (H,W) is the small side.  One block per written row.
@@ -323,7 +354,7 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
     const long long rows = (long long)B * (dst_is_hw ? H : OH);
     if (rows > 0x7fffffffLL || (long long)(dst_is_hw ? W : OW) * C > 0x7fffffffLL) return PDW_ERR_BAD_SHAPE;
     const unsigned blocks = (unsigned)rows;
-    const Shape s{B, H, W, C, OH, OW};
+    const Shape s{B, H, W, C, OH, OW, ld};
     const float sh = (float)H / (float)OH, sw = (float)W / (float)OW;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return with_type_and_width(dtype, v, [&](auto t, auto w) {
@@ -332,7 +363,7 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
         const T* in = static_cast<const T*>(src);
         T* out = static_cast<T*>(dst);
         if constexpr (OP == Resample::PoolFwd) pool_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s);
-        else if constexpr (OP == Resample::PoolBwd) pool_bwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+        else if constexpr (OP == Resample::PoolBwd) pool_bwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
         else if constexpr (OP == Resample::UpFwd) upsample_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
         else {
             const size_t table = sizeof(float) * (kMaxTaps + 2 + 2 * (size_t)W + (size_t)W * kMaxTaps);
@@ -368,12 +399,46 @@ int pdw_upsample_bwd(const void* go, void* dx, int B, int H, int W, int C, int O
     return run_resample<Resample::UpBwd>(go, dx, B, H, W, C, OH, OW, dtype, stream);
 }
 
-int pdw_gate_fwd(const void* a, void* y, int64_t pixels, int C, float inv_scale, int dtype, void* stream) {
+int pdw_pool_bwd_accumulate(const void* go, void* dx, int B, int H, int W, int C, int OH, int OW, int dtype, void* stream) {
+    return run_resample<Resample::PoolBwd>(go, dx, B, H, W, C, OH, OW, dtype, stream, 0, true);
+}
+int pdw_upsample_fwd_strided(const void* x, void* y, int B, int H, int W, int C, int OH, int OW, int ld_y, int dtype,
+                             void* stream) {
+    return run_resample<Resample::UpFwd>(x, y, B, H, W, C, OH, OW, dtype, stream, ld_y);
+}
+int pdw_upsample_bwd_strided(const void* go, void* dx, int B, int H, int W, int C, int OH, int OW, int ld_go, int dtype,
+                             void* stream) {
+    return run_resample<Resample::UpBwd>(go, dx, B, H, W, C, OH, OW, dtype, stream, ld_go);
+}
+
+int pdw_add_pooled(void* y, const void* v, int B, int64_t pixels_per_image, int C, float alpha, int dtype, void* stream) {
+    if (!y || !v) return PDW_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
+    if (B <= 0 || pixels_per_image <= 0 || C <= 0 || pixels_per_image > 0x7fffffffLL || B > 65535) return PDW_ERR_BAD_SHAPE;
+    if (!aligned_to(y, dtype_size(dtype)) || !aligned_to(v, dtype_size(dtype))) return PDW_ERR_MISALIGNED;
+    const int vw = vec_width(dtype, C, y, v);
+    // ~64 KB of y per block
+    int per_block = (int)(65536 / ((size_t)C * dtype_size(dtype)));
+    if (per_block < 1) per_block = 1;
+    const long long bx = (pixels_per_image + per_block - 1) / per_block;
+    if (bx > 0x7fffffffLL) return PDW_ERR_BAD_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid((unsigned)bx, (unsigned)B);
+    return with_type_and_width(dtype, vw, [&](auto t, auto w) {
+        using T = decltype(t);
+        constexpr int V = decltype(w)::value;
+        add_pooled_kernel<T, V><<<grid, kRowThreads, 0, st>>>(static_cast<T*>(y), static_cast<const T*>(v),
+                                                             (int)pixels_per_image, C, alpha, per_block);
+        return check_launch();
+    });
+}
+
+static int gate_fwd_impl(const void* a, void* y, int64_t pixels, int C, int ld_y, float inv_scale, int dtype, void* stream) {
     if (!a || !y) return PDW_ERR_NULL_POINTER;
     if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
-    if (pixels <= 0 || C <= 0 || (C % 2) != 0) return PDW_ERR_BAD_SHAPE;
+    if (pixels <= 0 || C <= 0 || (C % 2) != 0 || ld_y < C / 2) return PDW_ERR_BAD_SHAPE;
     if (!aligned_to(a, dtype_size(dtype)) || !aligned_to(y, dtype_size(dtype))) return PDW_ERR_MISALIGNED;
-    const int v = vec_width(dtype, C / 2, a, y);
+    const int v = (ld_y % (16 / (int)dtype_size(dtype)) == 0) ? vec_width(dtype, C / 2, a, y) : 1;
     const long long total = (long long)pixels * ((C / 2) / v);
     unsigned blocks;
     if (!grid_for(total, &blocks)) return PDW_ERR_BAD_SHAPE;
@@ -381,19 +446,27 @@ int pdw_gate_fwd(const void* a, void* y, int64_t pixels, int C, float inv_scale,
     return with_type_and_width(dtype, v, [&](auto t, auto w) {
         using T = decltype(t);
         constexpr int V = decltype(w)::value;
-        gate_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(static_cast<const T*>(a), static_cast<T*>(y), C, inv_scale, total);
+        gate_fwd_kernel<T, V><<<blocks, 256, 0, st>>>(static_cast<const T*>(a), static_cast<T*>(y), C, ld_y, inv_scale, total);
         return check_launch();
     });
 }
 
-int pdw_gate_bwd(const void* a, const void* gy, void* ga, int64_t pixels, int C, float inv_scale, int dtype,
-                 void* stream) {
+int pdw_gate_fwd(const void* a, void* y, int64_t pixels, int C, float inv_scale, int dtype, void* stream) {
+    return gate_fwd_impl(a, y, pixels, C, C / 2, inv_scale, dtype, stream);
+}
+int pdw_gate_fwd_strided(const void* a, void* y, int64_t pixels, int C, int ld_y, float inv_scale, int dtype,
+                         void* stream) {
+    return gate_fwd_impl(a, y, pixels, C, ld_y, inv_scale, dtype, stream);
+}
+
+static int gate_bwd_impl(const void* a, const void* gy, void* ga, int64_t pixels, int C, int ld_gy, float inv_scale,
+                         int dtype, void* stream) {
     if (!a || !gy || !ga) return PDW_ERR_NULL_POINTER;
     if (!dtype_ok(dtype)) return PDW_ERR_BAD_DTYPE;
-    if (pixels <= 0 || C <= 0 || (C % 2) != 0) return PDW_ERR_BAD_SHAPE;
+    if (pixels <= 0 || C <= 0 || (C % 2) != 0 || ld_gy < C / 2) return PDW_ERR_BAD_SHAPE;
     const size_t es = dtype_size(dtype);
     if (!aligned_to(a, es) || !aligned_to(gy, es) || !aligned_to(ga, es)) return PDW_ERR_MISALIGNED;
-    const int v = vec_width(dtype, C / 2, a, gy, ga);
+    const int v = (ld_gy % (16 / (int)es) == 0) ? vec_width(dtype, C / 2, a, gy, ga) : 1;
     const long long total = (long long)pixels * ((C / 2) / v);
     unsigned blocks;
     if (!grid_for(total, &blocks)) return PDW_ERR_BAD_SHAPE;
@@ -402,9 +475,18 @@ int pdw_gate_bwd(const void* a, const void* gy, void* ga, int64_t pixels, int C,
         using T = decltype(t);
         constexpr int V = decltype(w)::value;
         gate_bwd_kernel<T, V><<<blocks, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(gy),
-                                                      static_cast<T*>(ga), C, inv_scale, total);
+                                                      static_cast<T*>(ga), C, ld_gy, inv_scale, total);
         return check_launch();
     });
+}
+
+int pdw_gate_bwd(const void* a, const void* gy, void* ga, int64_t pixels, int C, float inv_scale, int dtype,
+                 void* stream) {
+    return gate_bwd_impl(a, gy, ga, pixels, C, C / 2, inv_scale, dtype, stream);
+}
+int pdw_gate_bwd_strided(const void* a, const void* gy, void* ga, int64_t pixels, int C, int ld_gy, float inv_scale,
+                         int dtype, void* stream) {
+    return gate_bwd_impl(a, gy, ga, pixels, C, ld_gy, inv_scale, dtype, stream);
 }
 
 }  // extern "C"

@@ -8,6 +8,7 @@ pyramid_dwconv/dwconv_triton.py:389-426).
 import torch
 from torch import nn
 
+from .block_function import ConvBlockFunction
 from .ops import (AdaptiveAvgPool2dFunction, BilinearInterp2dFunction, DepthwiseConv2DFunction, GateFunction, _pair)
 
 
@@ -108,6 +109,19 @@ class ConvBlock(nn.Module):
         self.conv_pool = nn.Linear(dim, dim, bias=out_bias)
 
     def forward(self, x):
+        dw = [g.conv_spatial for g in self.gates]
+        params = [self.conv_up.weight, self.conv_out.weight, self.conv_pool.weight] + [c.weight for c in dw]
+        fusable = (x.dim() == 4 and all(p.dtype == x.dtype for p in params)
+                   and all(c.bias is None and c.kernel_size[0] == c.kernel_size[1] for c in dw))
+        if not fusable:
+            return self.forward_unfused(x)
+        return ConvBlockFunction.apply(
+            x, tuple(g.scale_factor for g in self.gates), self.conv_up.weight, self.conv_up.bias,
+            self.conv_out.weight, self.conv_out.bias, self.conv_pool.weight, self.conv_pool.bias,
+            *[c.weight for c in dw])
+
+    def forward_unfused(self, x):
+        """The same block composed op by op, exactly as the reference writes it."""
         branches_in = self.conv_up(x)
         branches = torch.cat([gate(branches_in) for gate in self.gates], dim=-1)
         pooled = self.conv_pool(x.mean(dim=(1, 2), keepdim=True))

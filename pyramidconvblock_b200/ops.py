@@ -256,6 +256,110 @@ def upsample_backward(grad_out, input_hw):
     return _resample("pdw_upsample_bwd", grad_out, (B, H, W, C), H, W, OH, OW)
 
 
+def _slice_ld(t, channels, what):
+    """Pixel stride (elements) of a [..., channels] tensor that is dense or a channel slice of a
+    wider dense NHWC buffer; raises for any other layout."""
+    if t.shape[-1] != channels or t.stride(-1) != 1:
+        raise RuntimeError("%s must have %d contiguous channels" % (what, channels))
+    ld = t.stride(-2) if t.dim() >= 2 else channels
+    expect = ld
+    for d in range(t.dim() - 2, -1, -1):
+        if t.shape[d] != 1 and t.stride(d) != expect:
+            raise RuntimeError("%s must be dense NHWC or a channel slice of a dense NHWC buffer" % what)
+        expect *= t.shape[d]
+    return ld
+
+
+def gate_forward_into(conv_out, out_slice, inv_scale):
+    """gate_forward writing into ``out_slice``, a [..., C/2] channel slice of a wider NHWC buffer."""
+    _require_cuda(conv_out, out_slice)
+    conv_out = conv_out.contiguous()
+    C = conv_out.shape[-1]
+    pixels = conv_out.numel() // C
+    ld = _slice_ld(out_slice, C // 2, "output slice")
+    with torch.cuda.device(conv_out.device):
+        rc = _call("gate_fwd", (pixels, C), 1, conv_out.device, lambda: _lib.lib().pdw_gate_fwd_strided(
+            _ptr(conv_out), _ptr(out_slice), pixels, C, ld, float(inv_scale), _dtype_code(conv_out),
+            _stream(conv_out)))
+    _lib.check(rc, "pdw_gate_fwd_strided")
+    return out_slice
+
+
+def gate_backward_from(conv_out, grad_slice, inv_scale):
+    """gate_backward reading ``grad_slice``, a [..., C/2] channel slice of a wider NHWC gradient."""
+    _require_cuda(conv_out, grad_slice)
+    conv_out = conv_out.contiguous()
+    C = conv_out.shape[-1]
+    pixels = conv_out.numel() // C
+    ld = _slice_ld(grad_slice, C // 2, "gradient slice")
+    ga = torch.empty_like(conv_out)
+    with torch.cuda.device(conv_out.device):
+        rc = _call("gate_bwd", (pixels, C), 1, conv_out.device, lambda: _lib.lib().pdw_gate_bwd_strided(
+            _ptr(conv_out), _ptr(grad_slice), _ptr(ga), pixels, C, ld, float(inv_scale), _dtype_code(conv_out),
+            _stream(conv_out)))
+    _lib.check(rc, "pdw_gate_bwd_strided")
+    return ga
+
+
+def upsample_forward_into(x, out_slice):
+    """Bilinear resize of x[B,h,w,C] into ``out_slice`` [B,H,W,C], a channel slice of a wider buffer."""
+    _require_cuda(x, out_slice)
+    _check_nhwc(x, "input")
+    x = x.contiguous()
+    B, H, W, C = x.shape
+    OH, OW = out_slice.shape[1], out_slice.shape[2]
+    ld = _slice_ld(out_slice, C, "output slice")
+    with torch.cuda.device(x.device):
+        rc = _call("upsample_fwd", (B, H, W, C, OH, OW), 1, x.device, lambda: _lib.lib().pdw_upsample_fwd_strided(
+            _ptr(x), _ptr(out_slice), B, H, W, C, OH, OW, ld, _dtype_code(x), _stream(x)))
+    _lib.check(rc, "pdw_upsample_fwd_strided")
+    return out_slice
+
+
+def upsample_backward_from(grad_slice, input_hw):
+    """Adjoint of the resize reading ``grad_slice`` [B,H,W,C], a channel slice of a wider gradient."""
+    _require_cuda(grad_slice)
+    B, OH, OW, C = grad_slice.shape
+    H, W = input_hw
+    ld = _slice_ld(grad_slice, C, "gradient slice")
+    dx = torch.empty((B, H, W, C), device=grad_slice.device, dtype=grad_slice.dtype)
+    with torch.cuda.device(dx.device):
+        rc = _call("upsample_bwd", (B, H, W, C, OH, OW), 1, dx.device, lambda: _lib.lib().pdw_upsample_bwd_strided(
+            _ptr(grad_slice), _ptr(dx), B, H, W, C, OH, OW, ld, _dtype_code(dx), _stream(dx)))
+    _lib.check(rc, "pdw_upsample_bwd_strided")
+    return dx
+
+
+def pool_backward_accumulate(grad_out, dx):
+    """dx[B,H,W,C] += adjoint of the adaptive average pool applied to grad_out[B,OH,OW,C]."""
+    _require_cuda(grad_out, dx)
+    grad_out = grad_out.contiguous()
+    if not dx.is_contiguous():
+        raise RuntimeError("accumulation target must be contiguous")
+    B, OH, OW, C = grad_out.shape
+    H, W = dx.shape[1], dx.shape[2]
+    with torch.cuda.device(dx.device):
+        rc = _call("pool_bwd", (B, H, W, C, OH, OW), 1, dx.device, lambda: _lib.lib().pdw_pool_bwd_accumulate(
+            _ptr(grad_out), _ptr(dx), B, H, W, C, OH, OW, _dtype_code(dx), _stream(dx)))
+    _lib.check(rc, "pdw_pool_bwd_accumulate")
+    return dx
+
+
+def add_pooled_(y, v, alpha=1.0):
+    """In place y[b, ..., :] += alpha * v[b, :] (y: [B, ..., C] contiguous, v: [B, C])."""
+    _require_cuda(y, v)
+    if not y.is_contiguous():
+        raise RuntimeError("y must be contiguous")
+    v = v.contiguous()
+    B, C = y.shape[0], y.shape[-1]
+    pixels = y.numel() // (B * C)
+    with torch.cuda.device(y.device):
+        rc = _call("add_pooled", (B, pixels, C), 1, y.device, lambda: _lib.lib().pdw_add_pooled(
+            _ptr(y), _ptr(v), B, pixels, C, float(alpha), _dtype_code(y), _stream(y)))
+    _lib.check(rc, "pdw_add_pooled")
+    return y
+
+
 def gate_forward(conv_out, inv_scale):
     """y[..., :C/2] = x1 * (x2 * inv_scale) for conv_out = cat(x1, x2) on the last axis."""
     _require_cuda(conv_out)

@@ -57,6 +57,31 @@ def test_convblock_16bit_against_fp32_oracle(dtype):
         bar(p.grad, grads_ref[name], "grad " + name)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kwargs", [dict(), dict(bias=True), dict(scales=(1., 0.5, 0.25)), dict(scales=(0.5, 1.))])
+def test_fused_block_equals_op_by_op_composition(dtype, kwargs):
+    """ConvBlock.forward (one autograd Function, branches written into the concat buffer) against the
+    same block composed from the per-op Functions."""
+    torch.manual_seed(3)
+    m = ConvBlock(32, kernel_size=7, **kwargs).to(dtype).cuda()
+    (x,) = draw([(2, 16, 20, 32)], 6)
+    (go,) = draw([(2, 16, 20, 32)], 7)
+    results = []
+    for fn in (m.forward, m.forward_unfused):
+        xd = x.to(dtype).cuda().requires_grad_(True)
+        m.zero_grad(set_to_none=True)
+        y = fn(xd)
+        y.backward(go.to(dtype).cuda())
+        results.append([y.detach(), xd.grad] + [p.grad.clone() for p in m.parameters()])
+    names = ["y", "dx"] + [n for n, _ in m.named_parameters()]
+    for name, a, b in zip(names, *results):
+        a, b = a.float().cpu().numpy(), b.float().cpu().numpy()
+        if dtype == torch.float32:
+            assert_close_fp32(a, b, name, rtol=1e-5, atol_rel=2e-5)
+        else:
+            assert_close_16bit(a, b, name, rtol=2e-2, atol=2e-3 + 1e-2 * float(np.abs(b).max()))
+
+
 @pytest.mark.parametrize("scale_factor", [1.0, 0.5])
 def test_simple_gate_matches_oracle(scale_factor):
     torch.manual_seed(1)

@@ -235,3 +235,42 @@ def test_known_answers_on_gpu():
     const = torch.full((1, 9, 7, 8), 3.25).cuda()
     assert torch.allclose(ops.pool_forward(const, (4, 3)), torch.tensor(3.25).cuda())
     assert torch.allclose(ops.upsample_forward(const, (18, 15)), torch.tensor(3.25).cuda())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_slice_variants_and_accumulate(dtype):
+    """The *_strided entry points read/write a channel slice of a wider buffer in place; the results
+    equal the dense entry points on a contiguous copy of the slice, and nothing outside the slice is
+    touched.  pool_bwd_accumulate adds onto its target; add_pooled is a row-broadcast add."""
+    C, wide = 16, 40
+    conv, gy_wide, small, go_wide, tgt, v = draw(
+        [(2, 6, 7, 2 * C), (2, 6, 7, wide), (2, 3, 4, C), (2, 6, 7, wide), (2, 6, 7, C), (2, C)], 1200)
+    inv = 1.7
+    lo = 8   # slice [8, 8+C) of the wide buffer
+    convd, gyd, smalld, god = to_dev(conv, dtype), to_dev(gy_wide, dtype), to_dev(small, dtype), to_dev(go_wide, dtype)
+    # forward into a slice
+    buf = torch.full((2, 6, 7, wide), 7.0, device="cuda", dtype=dtype)
+    ops.gate_forward_into(convd, buf[..., lo:lo + C], inv)
+    assert torch.equal(buf[..., lo:lo + C], ops.gate_forward(convd, inv))
+    assert bool((buf[..., :lo] == 7).all()) and bool((buf[..., lo + C:] == 7).all())
+    buf.fill_(7.0)
+    ops.upsample_forward_into(smalld, buf[..., lo:lo + C])
+    assert torch.equal(buf[..., lo:lo + C], ops.upsample_forward(smalld, (6, 7)))
+    assert bool((buf[..., :lo] == 7).all()) and bool((buf[..., lo + C:] == 7).all())
+    # backward from a slice
+    gslice = gyd[..., lo:lo + C]
+    assert torch.equal(ops.gate_backward_from(convd, gslice, inv), ops.gate_backward(convd, gslice.contiguous(), inv))
+    gslice = god[..., lo:lo + C]
+    assert torch.equal(ops.upsample_backward_from(gslice, (3, 4)), ops.upsample_backward(gslice.contiguous(), (3, 4)))
+    # accumulate and broadcast add against the oracle / plain arithmetic
+    chk = close(dtype)
+    tgtd = to_dev(tgt, dtype)
+    ops.pool_backward_accumulate(smalld, tgtd)
+    ref = rounded(tgt, dtype).numpy() + oracle.c_pool_bwd(rounded(small, dtype).numpy(), (6, 7))
+    chk(tgtd.float().cpu().numpy(), ref, "pool_bwd_accumulate")
+    yd = to_dev(tgt, dtype)
+    ops.add_pooled_(yd, to_dev(v, dtype), 0.25)
+    ref = rounded(tgt, dtype).double() + 0.25 * rounded(v, dtype).double()[:, None, None, :]
+    chk(yd.float().cpu().numpy(), ref.numpy(), "add_pooled")
+    with pytest.raises(RuntimeError):
+        ops.gate_forward_into(convd, buf[..., lo:lo + C].permute(0, 2, 1, 3), inv)
