@@ -80,7 +80,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -235,6 +235,7 @@ def extra_sweeps(device):
                          ("bwd_weight_bias", lambda: ops.dwconv_backward_weight(x, go, k, 1, k // 2, 1, with_bias=True))):
             ms = timed(fn)
             rec[name] = {"ms": round(ms, 4), "frac_fp32_peak": round(2 * fma / (ms * 1e-3) / 1e12 / peaks["fp32_tflops"], 4)}
+        rec["dwconv_fwd_bwd_ms"] = round(rec["fwd"]["ms"] + rec["bwd_input"]["ms"] + rec["bwd_weight_bias"]["ms"], 4)
         torch.manual_seed(0)
         m = ConvBlock(256, kernel_size=k).to(torch.float16).to(device)
         xg = x.clone().requires_grad_(True)
@@ -247,6 +248,71 @@ def extra_sweeps(device):
 
         rec["convblock256_fwd_bwd_ms"] = round(timed(block_step, n=5, warm=2), 4)
         out["k%d" % k] = rec
+    return out
+
+
+def reference_triton_timings(device):
+    """Times the UNMODIFIED reference package (its Triton kernels, JIT-compiled for this GPU) on the
+    same single-GPU shapes as extra_sweeps(), if an untracked copy of it sits in baseline/_ref/ (put
+    there by __graft_entry__.build()).  Every shape is warmed up twice first: the reference autotunes
+    on the first call, and its weight-gradient kernel accumulates into its output while tuning."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "pyramid_dwconv_reference")):
+        return {"unavailable": "no copy of the reference package under baseline/_ref"}
+    try:
+        sys.path.insert(0, ref_dir)
+        import pyramid_dwconv_reference as ref
+    except Exception as e:   # triton missing, import error
+        return {"unavailable": "reference import failed: %s" % (str(e).splitlines()[0][:120],)}
+    finally:
+        sys.path.remove(ref_dir)
+
+    def timed(fn, n=5, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / n
+
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn((16, 128, 128, 256), generator=gen, device=device).half()
+    go = torch.randn((16, 128, 128, 256), generator=gen, device=device).half()
+    try:
+        for k in (9, 13, 17):
+            w = (torch.randn((k, k, 256), generator=gen, device=device) / k).half().requires_grad_(True)
+            xg = x.clone().requires_grad_(True)
+            p = (k // 2, k // 2)
+            F = ref.DepthwiseConv2DFunction
+
+            def fwd():
+                with torch.no_grad():
+                    F.apply(x, w, (1, 1), p, (1, 1), torch.float16)
+
+            def fwd_bwd():
+                xg.grad = None
+                w.grad = None
+                F.apply(xg, w, (1, 1), p, (1, 1), torch.float16).backward(go)
+
+            rec = {"dwconv_fwd_ms": round(timed(fwd), 4), "dwconv_fwd_bwd_ms": round(timed(fwd_bwd), 4)}
+            torch.manual_seed(0)
+            m = ref.ConvBlock(256, kernel_size=k).to(torch.float16).to(device)
+
+            def block_step():
+                xg.grad = None
+                for q in m.parameters():
+                    q.grad = None
+                m(xg).backward(go)
+
+            rec["convblock256_fwd_bwd_ms"] = round(timed(block_step, n=5, warm=3), 4)
+            out["k%d" % k] = rec
+    except Exception as e:
+        out["error"] = str(e).splitlines()[0][:200]
     return out
 
 
@@ -432,6 +498,7 @@ def main():
         result["cpu_baseline"] = time_cpu_reference()
     if world == 1 and not args.no_extra:
         result["extra"] = extra_sweeps(device)
+        result["extra"]["reference_triton_same_gpu"] = reference_triton_timings(device)
     print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
