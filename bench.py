@@ -460,7 +460,7 @@ def main():
     dom_flops = 2 * conv_fmas(*dom_shape)
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12 if dom_calls else None
     # DRAM traffic of one launch from the ncu capture summarised in profiles/ (bytes per image of
-    # [96,96,256] bf16, scaled by the images one launch processes); None until captured.
+    # [96,96,256] bf16, scaled by the images one launch processes).
     traffic_per_image = TRAFFIC_BYTES_PER_IMAGE
     roofline = {
         "kernel": "dwconv_tiled_kernel<bf16,K=17> (forward and input gradient, gate 0: [%d,96,96,256])" % local_b,
@@ -505,8 +505,8 @@ def main():
 
 
 # DRAM bytes (read + write) of one dwconv_tiled_kernel launch per image of [96,96,256] bf16, k=17,
-# from the ncu capture summarised under profiles/; None until that capture exists.
-TRAFFIC_BYTES_PER_IMAGE = None
+# from the ncu capture summarised under profiles/ (traffic grows in proportion to the images of a launch).
+TRAFFIC_BYTES_PER_IMAGE = 8.36e6   # 267.6 MB for 32 images (profiles/dwconv_tiled_fwd_k17_bf16_32x96x96x256.md)
 
 if __name__ == "__main__":
     main()
