@@ -40,25 +40,52 @@ constexpr int kRowThreads = 256;
 // the vector index fastest, so a warp touches consecutive 16-byte pieces of consecutive pixels, and all
 // index arithmetic is 32-bit.
 
+// Walks the (column, channel vector) pairs of one row, vector index fastest, without a division per
+// step: thread t starts at pair t and advances by the block size.
+struct RowWalker {
+    int col, vec;          // current column and channel-vector index
+    int dcol, dvec, cv;    // advance per step, vectors per pixel
+    __device__ __forceinline__ RowWalker(int cv_, int start, int step) : cv(cv_) {
+        col = start / cv_;  vec = start - col * cv_;
+        dcol = step / cv_;  dvec = step - dcol * cv_;
+    }
+    __device__ __forceinline__ void next() {
+        col += dcol;  vec += dvec;
+        if (vec >= cv) { vec -= cv; ++col; }
+    }
+};
+
 // ---- adaptive average pool ------------------------------------------------------------------
-template <typename T, int V>
+// TAB: the window of every output column is looked up in a shared-memory table built once per block
+// (the host uses it whenever the table fits); otherwise it is computed per access.
+template <typename T, int V, bool TAB>
 __global__ void __launch_bounds__(kRowThreads) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s) {
+    extern __shared__ int itab[];                     // [OW] window start, [OW] window length
     const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
-    const int cv = s.C / V, n = s.OW * cv;
+    const int cv = s.C / V;
     const int hs = win_start(oh, s.H, s.OH), he = win_end(oh, s.H, s.OH);
+    if (TAB) {
+        for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads) {
+            const int ws = win_start(ow, s.W, s.OW);
+            itab[ow] = ws;
+            itab[s.OW + ow] = win_end(ow, s.W, s.OW) - ws;
+        }
+        __syncthreads();
+    }
     const T* xin = x + ((size_t)b * s.H + hs) * s.W * s.C;
     T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.C;
     const size_t row_stride = (size_t)s.W * s.C;
-    for (int t = threadIdx.x; t < n; t += kRowThreads) {
-        const int ow = t / cv, c = (t - ow * cv) * V;
-        const int ws = win_start(ow, s.W, s.OW), we = win_end(ow, s.W, s.OW);
+    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.OW; w.next()) {
+        const int ow = w.col, c = w.vec * V;
+        const int ws = TAB ? itab[ow] : win_start(ow, s.W, s.OW);
+        const int nw = TAB ? itab[s.OW + ow] : win_end(ow, s.W, s.OW) - ws;
         float acc[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
         const T* p = xin + (size_t)ws * s.C + c;
         for (int ih = hs; ih < he; ++ih, p += row_stride)
-            for (int iw = 0; iw < we - ws; ++iw) load_acc<T, V>(p + (size_t)iw * s.C, acc, 1.f);
-        const float inv = 1.f / (float)((he - hs) * (we - ws));
+            for (int iw = 0; iw < nw; ++iw) load_acc<T, V>(p + (size_t)iw * s.C, acc, 1.f);
+        const float inv = 1.f / (float)((he - hs) * nw);
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] *= inv;
         store_vec<T, V>(yrow + (size_t)ow * s.C + c, acc);
@@ -67,25 +94,39 @@ __global__ void __launch_bounds__(kRowThreads) pool_fwd_kernel(const T* __restri
 
 // dx[ih,iw] = sum over the outputs whose window holds (ih,iw) of grad_out / window area.  The
 // outputs that hold input index i are exactly [floor(i*out/in), ceil((i+1)*out/in)).
-template <typename T, int V>
+template <typename T, int V, bool TAB>
 __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
                                                                const bool accumulate) {
+    extern __shared__ int itab[];     // [W] first output column, [W] count, then float [OW] 1/window width
+    float* inv_kw = reinterpret_cast<float*>(itab + 2 * s.W);
     const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
-    const int cv = s.C / V, n = s.W * cv;
+    const int cv = s.C / V;
     const int oh0 = win_start(ih, s.OH, s.H), oh1 = win_end(ih, s.OH, s.H);
+    if (TAB) {
+        for (int iw = threadIdx.x; iw < s.W; iw += kRowThreads) {
+            const int o0 = win_start(iw, s.OW, s.W);
+            itab[iw] = o0;
+            itab[s.W + iw] = win_end(iw, s.OW, s.W) - o0;
+        }
+        for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads)
+            inv_kw[ow] = 1.f / (float)(win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW));
+        __syncthreads();
+    }
     T* drow = dx + ((size_t)b * s.H + ih) * s.W * s.C;
-    for (int t = threadIdx.x; t < n; t += kRowThreads) {
-        const int iw = t / cv, c = (t - iw * cv) * V;
-        const int ow0 = win_start(iw, s.OW, s.W), ow1 = win_end(iw, s.OW, s.W);
+    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.W; w.next()) {
+        const int iw = w.col, c = w.vec * V;
+        const int ow0 = TAB ? itab[iw] : win_start(iw, s.OW, s.W);
+        const int now = TAB ? itab[s.W + iw] : win_end(iw, s.OW, s.W) - ow0;
         float acc[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
         for (int oh = oh0; oh < oh1; ++oh) {
-            const int kh = win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH);
-            const T* row = go + (((size_t)b * s.OH + oh) * s.OW) * s.C + c;
-            for (int ow = ow0; ow < ow1; ++ow) {
-                const int kw = win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW);
-                load_acc<T, V>(row + (size_t)ow * s.C, acc, 1.f / (float)(kh * kw));
+            const float inv_kh = 1.f / (float)(win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH));
+            const T* row = go + (((size_t)b * s.OH + oh) * s.OW + ow0) * s.C + c;
+            for (int j = 0; j < now; ++j) {
+                const float ikw = TAB ? inv_kw[ow0 + j]
+                                      : 1.f / (float)(win_end(ow0 + j, s.W, s.OW) - win_start(ow0 + j, s.W, s.OW));
+                load_acc<T, V>(row + (size_t)j * s.C, acc, inv_kh * ikw);
             }
         }
         if (accumulate) load_acc<T, V>(drow + (size_t)iw * s.C + c, acc, 1.f);   // dx += ...
@@ -108,19 +149,26 @@ __device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
     return t;
 }
 
-// s.H,s.W: source extent (small), s.OH,s.OW: destination extent.
-template <typename T, int V>
+// s.H,s.W: source extent (small), s.OH,s.OW: destination extent.  TAB: the two source columns and
+// weights of every destination column come from a shared-memory table built once per block.
+template <typename T, int V, bool TAB>
 __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s,
                                                                    float scale_h, float scale_w) {
+    extern __shared__ int itab[];                 // [OW] x {i0, i1, l0, l1}
+    Tap* xt = reinterpret_cast<Tap*>(itab);
     const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
-    const int cv = s.C / V, n = s.OW * cv;
+    const int cv = s.C / V;
+    if (TAB) {
+        for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads) xt[ow] = source_taps(ow, scale_w, s.W);
+        __syncthreads();
+    }
     const Tap ty = source_taps(oh, scale_h, s.H);
     const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C;
     const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C;
     T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.ld;
-    for (int t = threadIdx.x; t < n; t += kRowThreads) {
-        const int ow = t / cv, c = (t - ow * cv) * V;
-        const Tap tx = source_taps(ow, scale_w, s.W);
+    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.OW; w.next()) {
+        const int ow = w.col, c = w.vec * V;
+        const Tap tx = TAB ? xt[ow] : source_taps(ow, scale_w, s.W);
         float acc[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
@@ -180,12 +228,12 @@ __global__ void __launch_bounds__(kRowThreads) upsample_bwd_kernel(const T* __re
     }
     __syncthreads();
     const int oy0 = meta[0], ny = meta[1];
-    const int cv = s.C / V, n = s.W * cv;
+    const int cv = s.C / V;
     const T* gbase = go + ((size_t)b * s.OH + oy0) * s.OW * s.ld;
     const size_t row_stride = (size_t)s.OW * s.ld;
     T* drow = dx + ((size_t)b * s.H + iy) * s.W * s.C;
-    for (int t = threadIdx.x; t < n; t += kRowThreads) {
-        const int ix = t / cv, c = (t - ix * cv) * V;
+    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.W; w.next()) {
+        const int ix = w.col, c = w.vec * V;
         const int ox0 = meta[2 + 2 * ix], nx = meta[3 + 2 * ix];
         const float* wxi = wx + ix * kMaxTaps;
         float acc[V];
@@ -362,10 +410,20 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
         constexpr int V = decltype(w)::value;
         const T* in = static_cast<const T*>(src);
         T* out = static_cast<T*>(dst);
-        if constexpr (OP == Resample::PoolFwd) pool_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s);
-        else if constexpr (OP == Resample::PoolBwd) pool_bwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
-        else if constexpr (OP == Resample::UpFwd) upsample_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
-        else {
+        [[maybe_unused]] constexpr size_t kTableMax = 40 * 1024;   // lookup tables must fit the default shared memory
+        if constexpr (OP == Resample::PoolFwd) {
+            const size_t tab = sizeof(int) * 2 * (size_t)OW;
+            if (tab <= kTableMax) pool_fwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s);
+            else pool_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+        } else if constexpr (OP == Resample::PoolBwd) {
+            const size_t tab = sizeof(int) * (2 * (size_t)W + (size_t)OW);
+            if (tab <= kTableMax) pool_bwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
+            else pool_bwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
+        } else if constexpr (OP == Resample::UpFwd) {
+            const size_t tab = sizeof(Tap) * (size_t)OW;
+            if (tab <= kTableMax) upsample_fwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s, sh, sw);
+            else upsample_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
+        } else {
             const size_t table = sizeof(float) * (kMaxTaps + 2 + 2 * (size_t)W + (size_t)W * kMaxTaps);
             if (max_taps_per_source(H, OH) <= kMaxTaps && max_taps_per_source(W, OW) <= kMaxTaps && table <= 40 * 1024) {
                 upsample_bwd_kernel<T, V><<<blocks, kRowThreads, table, st>>>(in, out, s, sh, sw);
