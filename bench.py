@@ -248,6 +248,58 @@ def extra_sweeps(device):
 
         rec["convblock256_fwd_bwd_ms"] = round(timed(block_step, n=5, warm=2), 4)
         out["k%d" % k] = rec
+    del x, go
+    out["chain256_k13_fp16"] = literal_chain_timing(device, timed, peaks)
+    out["pyramid_bf16_32x128x128x384"] = pyramid_timings(device, timed, peaks)
+    return out
+
+
+def literal_chain_timing(device, timed, peaks):
+    """pool 128->64, depthwise conv k=13 with bias at C=256, bilinear upsample back to 128, forward and
+    backward (dX, dW[13,13,256], dbias[256]) on fp16 [16,128,128,256], through the per-op Functions."""
+    from pyramidconvblock_b200 import AdaptiveAvgPool2dFunction, BilinearInterp2dFunction, DepthwiseConv2DFunction
+    gen = torch.Generator(device=device).manual_seed(2)
+    x = torch.randn((16, 128, 128, 256), generator=gen, device=device).half().requires_grad_(True)
+    go = torch.randn((16, 128, 128, 256), generator=gen, device=device).half()
+    w = (torch.randn((13, 13, 256), generator=gen, device=device) / 13).half().requires_grad_(True)
+    b = (torch.randn((256,), generator=gen, device=device) * 0.1).half().requires_grad_(True)
+
+    def step():
+        x.grad = w.grad = b.grad = None
+        t = AdaptiveAvgPool2dFunction.apply(x, (64, 64))
+        t = DepthwiseConv2DFunction.apply(t, w, (1, 1), (6, 6), (1, 1), torch.float16, b)
+        BilinearInterp2dFunction.apply(t, (128, 128)).backward(go)
+
+    ms = timed(step, n=10, warm=3)
+    fmas = 3 * conv_fmas(16, 64, 64, 256, 13)
+    n_f, n_h = 16 * 128 * 128 * 256, 16 * 64 * 64 * 256
+    per_op_bytes = (4 * n_f + 9 * n_h) * 2
+    t_fma = fmas / (peaks["fp32_tflops"] * 1e12 / 2) * 1e3
+    t_hbm = per_op_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+    return {"fwd_bwd_ms": round(ms, 4), "roofline_ms": round(max(t_fma, t_hbm), 4),
+            "frac_of_roofline": round(max(t_fma, t_hbm) / ms, 4),
+            "fma_time_at_peak_ms": round(t_fma, 4), "hbm_time_at_peak_ms_per_op_bytes": round(t_hbm, 4)}
+
+
+def pyramid_timings(device, timed, peaks):
+    """Adaptive average pool to 64/32/16 and bilinear upsample back to 128, forward and backward, each op
+    alone on bf16 [32,128,128,384]; algorithmic bytes = big tensor + small tensor, once each."""
+    from pyramidconvblock_b200 import ops
+    gen = torch.Generator(device=device).manual_seed(3)
+    x = (torch.rand((32, 128, 128, 384), generator=gen, device=device) * 2 - 1).bfloat16()
+    g = torch.randn((32, 128, 128, 384), generator=gen, device=device).bfloat16()
+    out = {}
+    for s in (64, 32, 16):
+        small = ops.pool_forward(x, (s, s))
+        byts = (x.numel() + small.numel()) * 2
+        rec = {}
+        for name, fn in (("pool_fwd", lambda: ops.pool_forward(x, (s, s))),
+                         ("upsample_fwd", lambda: ops.upsample_forward(small, (128, 128))),
+                         ("upsample_bwd", lambda: ops.upsample_backward(g, (s, s))),
+                         ("pool_bwd", lambda: ops.pool_backward(small, (128, 128)))):
+            ms = timed(fn, n=10, warm=3)
+            rec[name] = {"ms": round(ms, 4), "frac_hbm_peak": round(byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+        out["s%d" % s] = rec
     return out
 
 
