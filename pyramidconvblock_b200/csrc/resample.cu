@@ -36,9 +36,57 @@ struct Shape { int B, H, W, C, OH, OW, ld; };
 constexpr int kRowThreads = 256;
 
 // Every spatial kernel below runs one thread block per written row (b, row): what depends on the row
-// alone is computed once, the threads then sweep the row's (column, 16-byte channel vector) pairs with
-// the vector index fastest, so a warp touches consecutive 16-byte pieces of consecutive pixels, and all
-// index arithmetic is 32-bit.
+// alone is computed once per block, per-column windows / taps come from shared-memory tables built
+// once per block, and a thread keeps ONE channel vector and walks over columns, so the sweep is
+// loads, FMAs and one 16-byte store with 32-bit index arithmetic.  A warp covers consecutive 16-byte
+// pieces of one pixel (or of neighbouring pixels when a pixel has fewer than 32 vectors).
+struct RowThread {
+    int vec0, cvb;       // first channel vector of this thread, vectors handled per sweep
+    int lane, lanes;     // column lane of this thread, number of column lanes (lane >= lanes: idle)
+};
+__device__ __forceinline__ RowThread row_thread(int cv) {
+    RowThread r;
+    r.cvb = cv < kRowThreads ? cv : kRowThreads;
+    r.lanes = kRowThreads / r.cvb;
+    r.lane = (int)threadIdx.x / r.cvb;
+    r.vec0 = (int)threadIdx.x - r.lane * r.cvb;
+    return r;
+}
+
+template <typename T, int V>
+__device__ __forceinline__ Vec<T, V> ldv(const T* p) { return *reinterpret_cast<const Vec<T, V>*>(p); }
+template <typename T, int V>
+__device__ __forceinline__ void fma_vec(float (&acc)[V], const Vec<T, V>& d, float w) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = fmaf(Elem<T>::to_f(d.v[i]), w, acc[i]);
+}
+// acc += sum_{k<n} w * p[k*stride], loads issued four at a time so that several are in flight.
+template <typename T, int V>
+__device__ __forceinline__ void acc_run(float (&acc)[V], const T* p, int stride, int n, float w) {
+    for (int k0 = 0; k0 < n; k0 += 4) {
+        Vec<T, V> d[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (k0 + u < n) d[u] = ldv<T, V>(p + (k0 + u) * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (k0 + u < n) fma_vec<T, V>(acc, d[u], w);
+    }
+}
+// Same with one weight per element of the run: w[k] * wscale.
+template <typename T, int V>
+__device__ __forceinline__ void acc_run_weighted(float (&acc)[V], const T* p, int stride, int n, const float* w,
+                                                 float wscale) {
+    for (int k0 = 0; k0 < n; k0 += 4) {
+        Vec<T, V> d[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (k0 + u < n) d[u] = ldv<T, V>(p + (k0 + u) * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (k0 + u < n) fma_vec<T, V>(acc, d[u], w[k0 + u] * wscale);
+    }
+}
 
 // Walks the (column, channel vector) pairs of one row, vector index fastest, without a division per
 // step: thread t starts at pair t and advances by the block size.
@@ -94,11 +142,13 @@ __global__ void __launch_bounds__(kRowThreads) pool_fwd_kernel(const T* __restri
 
 // dx[ih,iw] = sum over the outputs whose window holds (ih,iw) of grad_out / window area.  The
 // outputs that hold input index i are exactly [floor(i*out/in), ceil((i+1)*out/in)).
+constexpr int kMaxPoolRows = 16;     // output rows that can hold one input row, for the table variant
 template <typename T, int V, bool TAB>
 __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
                                                                const bool accumulate) {
-    extern __shared__ int itab[];     // [W] first output column, [W] count, then float [OW] 1/window width
+    extern __shared__ int itab[];     // [W] first output column, [W] count, float [OW] 1/width, float [16] 1/height
     float* inv_kw = reinterpret_cast<float*>(itab + 2 * s.W);
+    float* inv_kh_tab = inv_kw + s.OW;
     const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
     const int cv = s.C / V;
     const int oh0 = win_start(ih, s.OH, s.H), oh1 = win_end(ih, s.OH, s.H);
@@ -110,6 +160,9 @@ __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restri
         }
         for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads)
             inv_kw[ow] = 1.f / (float)(win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW));
+        if ((int)threadIdx.x < oh1 - oh0 && threadIdx.x < kMaxPoolRows)
+            inv_kh_tab[threadIdx.x] =
+                1.f / (float)(win_end(oh0 + threadIdx.x, s.H, s.OH) - win_start(oh0 + threadIdx.x, s.H, s.OH));
         __syncthreads();
     }
     T* drow = dx + ((size_t)b * s.H + ih) * s.W * s.C;
@@ -121,7 +174,8 @@ __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restri
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
         for (int oh = oh0; oh < oh1; ++oh) {
-            const float inv_kh = 1.f / (float)(win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH));
+            const float inv_kh = TAB ? inv_kh_tab[oh - oh0]
+                                     : 1.f / (float)(win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH));
             const T* row = go + (((size_t)b * s.OH + oh) * s.OW + ow0) * s.C + c;
             for (int j = 0; j < now; ++j) {
                 const float ikw = TAB ? inv_kw[ow0 + j]
@@ -150,7 +204,8 @@ __device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
 }
 
 // s.H,s.W: source extent (small), s.OH,s.OW: destination extent.  TAB: the two source columns and
-// weights of every destination column come from a shared-memory table built once per block.
+// weights of every destination column come from a shared-memory table built once per block.  Two
+// destination columns per step: eight independent 16-byte loads in flight per thread.
 template <typename T, int V, bool TAB>
 __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s,
                                                                    float scale_h, float scale_w) {
@@ -162,21 +217,41 @@ __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __re
         for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads) xt[ow] = source_taps(ow, scale_w, s.W);
         __syncthreads();
     }
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
     const Tap ty = source_taps(oh, scale_h, s.H);
     const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C;
     const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C;
     T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.ld;
-    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.OW; w.next()) {
-        const int ow = w.col, c = w.vec * V;
-        const Tap tx = TAB ? xt[ow] : source_taps(ow, scale_w, s.W);
-        float acc[V];
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        const int c = vec * V;
+        for (int ow = rt.lane; ow < s.OW; ow += 2 * rt.lanes) {
+            const int ow2 = ow + rt.lanes;
+            const bool two = ow2 < s.OW;
+            const Tap ta = TAB ? xt[ow] : source_taps(ow, scale_w, s.W);
+            const Tap tb = two ? (TAB ? xt[ow2] : source_taps(ow2, scale_w, s.W)) : ta;
+            const Vec<T, V> a00 = ldv<T, V>(r0 + ta.i0 * s.C + c), a01 = ldv<T, V>(r0 + ta.i1 * s.C + c);
+            const Vec<T, V> a10 = ldv<T, V>(r1 + ta.i0 * s.C + c), a11 = ldv<T, V>(r1 + ta.i1 * s.C + c);
+            const Vec<T, V> b00 = ldv<T, V>(r0 + tb.i0 * s.C + c), b01 = ldv<T, V>(r0 + tb.i1 * s.C + c);
+            const Vec<T, V> b10 = ldv<T, V>(r1 + tb.i0 * s.C + c), b11 = ldv<T, V>(r1 + tb.i1 * s.C + c);
+            float acc[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = 0.f;
-        load_acc<T, V>(r0 + (size_t)tx.i0 * s.C + c, acc, ty.l0 * tx.l0);
-        load_acc<T, V>(r0 + (size_t)tx.i1 * s.C + c, acc, ty.l0 * tx.l1);
-        load_acc<T, V>(r1 + (size_t)tx.i0 * s.C + c, acc, ty.l1 * tx.l0);
-        load_acc<T, V>(r1 + (size_t)tx.i1 * s.C + c, acc, ty.l1 * tx.l1);
-        store_vec<T, V>(yrow + (size_t)ow * s.ld + c, acc);
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+            fma_vec<T, V>(acc, a00, ty.l0 * ta.l0);
+            fma_vec<T, V>(acc, a01, ty.l0 * ta.l1);
+            fma_vec<T, V>(acc, a10, ty.l1 * ta.l0);
+            fma_vec<T, V>(acc, a11, ty.l1 * ta.l1);
+            store_vec<T, V>(yrow + ow * s.ld + c, acc);
+            if (two) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = 0.f;
+                fma_vec<T, V>(acc, b00, ty.l0 * tb.l0);
+                fma_vec<T, V>(acc, b01, ty.l0 * tb.l1);
+                fma_vec<T, V>(acc, b10, ty.l1 * tb.l0);
+                fma_vec<T, V>(acc, b11, ty.l1 * tb.l1);
+                store_vec<T, V>(yrow + ow2 * s.ld + c, acc);
+            }
+        }
     }
 }
 
@@ -229,22 +304,22 @@ __global__ void __launch_bounds__(kRowThreads) upsample_bwd_kernel(const T* __re
     __syncthreads();
     const int oy0 = meta[0], ny = meta[1];
     const int cv = s.C / V;
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
     const T* gbase = go + ((size_t)b * s.OH + oy0) * s.OW * s.ld;
-    const size_t row_stride = (size_t)s.OW * s.ld;
+    const int row_stride = s.OW * s.ld;
     T* drow = dx + ((size_t)b * s.H + iy) * s.W * s.C;
-    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.W; w.next()) {
-        const int ix = w.col, c = w.vec * V;
-        const int ox0 = meta[2 + 2 * ix], nx = meta[3 + 2 * ix];
-        const float* wxi = wx + ix * kMaxTaps;
-        float acc[V];
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        for (int ix = rt.lane; ix < s.W; ix += rt.lanes) {
+            const int ox0 = meta[2 + 2 * ix], nx = meta[3 + 2 * ix];
+            const float* wxi = wx + ix * kMaxTaps;
+            float acc[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = 0.f;
-        const T* p = gbase + (size_t)ox0 * s.ld + c;
-        for (int jy = 0; jy < ny; ++jy, p += row_stride) {
-            const float wyj = wy[jy];
-            for (int jx = 0; jx < nx; ++jx) load_acc<T, V>(p + (size_t)jx * s.ld, acc, wyj * wxi[jx]);
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+            const T* p = gbase + ox0 * s.ld + vec * V;
+            for (int jy = 0; jy < ny; ++jy, p += row_stride) acc_run_weighted<T, V>(acc, p, s.ld, nx, wxi, wy[jy]);
+            store_vec<T, V>(drow + ix * s.C + vec * V, acc);
         }
-        store_vec<T, V>(drow + (size_t)ix * s.C + c, acc);
     }
 }
 
@@ -400,7 +475,9 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
     // Pool: (H,W) is the big side.  Upsample: (H,W) is the small side.  One block per written row.
     const bool dst_is_hw = pool ? !writes_small : writes_small;
     const long long rows = (long long)B * (dst_is_hw ? H : OH);
-    if (rows > 0x7fffffffLL || (long long)(dst_is_hw ? W : OW) * C > 0x7fffffffLL) return PDW_ERR_BAD_SHAPE;
+    // offsets inside one image are 32-bit in the kernels
+    if (rows > 0x7fffffffLL || (long long)H * W * ld > 0x7fffffffLL || (long long)OH * OW * ld > 0x7fffffffLL)
+        return PDW_ERR_BAD_SHAPE;
     const unsigned blocks = (unsigned)rows;
     const Shape s{B, H, W, C, OH, OW, ld};
     const float sh = (float)H / (float)OH, sw = (float)W / (float)OW;
@@ -416,8 +493,8 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
             if (tab <= kTableMax) pool_fwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s);
             else pool_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s);
         } else if constexpr (OP == Resample::PoolBwd) {
-            const size_t tab = sizeof(int) * (2 * (size_t)W + (size_t)OW);
-            if (tab <= kTableMax) pool_bwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
+            const size_t tab = sizeof(int) * (2 * (size_t)W + (size_t)OW + kMaxPoolRows);
+            if (tab <= kTableMax && (OH + H - 1) / H + 1 <= kMaxPoolRows) pool_bwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
             else pool_bwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
         } else if constexpr (OP == Resample::UpFwd) {
             const size_t tab = sizeof(Tap) * (size_t)OW;
