@@ -19,6 +19,61 @@ import torch.nn.functional as F
 from . import ops
 
 
+# Optional callback, set by the data-parallel helper: called from inside backward with
+# [(parameter, gradient), ...] as soon as every parameter gradient except conv_up's is final, i.e.
+# before the last two GEMMs of the backward pass, so that their reduction across ranks can overlap
+# with those GEMMs.
+early_gradient_hook = None
+
+# The reduced-resolution branches run on a second CUDA stream beside the full-resolution ones: their
+# kernels are small, and interleaving the two streams fills the ragged ends of each other's grids
+# (worth most when the per-GPU batch is small).  Set to False to keep everything on one stream.
+overlap_branches = True
+_side_streams = {}
+
+
+def _side_stream(device):
+    key = torch.device(device).index
+    st = _side_streams.get(key)
+    if st is None:
+        st = torch.cuda.Stream(device=device)
+        _side_streams[key] = st
+    return st
+
+
+class _Fork:
+    """Runs the enclosed region on the side stream, ordered after everything enqueued so far on the
+    current stream; join() makes the current stream wait for it and hands the tensors produced there
+    over to the current stream (the caching allocator must know about the second user)."""
+
+    def __init__(self, device, enabled, inputs):
+        self.enabled = enabled
+        if enabled:
+            self.main = torch.cuda.current_stream(device)
+            self.side = _side_stream(device)
+            self.ctx = torch.cuda.stream(self.side)
+            self.inputs = inputs
+
+    def __enter__(self):
+        if self.enabled:
+            self.side.wait_stream(self.main)
+            for t in self.inputs:
+                t.record_stream(self.side)
+            self.ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            self.ctx.__exit__(*exc)
+
+    def join(self, produced):
+        if self.enabled:
+            self.main.wait_stream(self.side)
+            for t in produced:
+                if t is not None:
+                    t.record_stream(self.main)
+
+
 class ConvBlockFunction(torch.autograd.Function):
     """apply(x, scales, w_up, b_up, w_out, b_out, w_pool, b_pool, *dw_weights) -> y, all [B,H,W,*] NHWC."""
 
@@ -31,19 +86,26 @@ class ConvBlockFunction(torch.autograd.Function):
         inv_scale = 1.0 / (inter / 2) ** -0.5
         t = F.linear(x, w_up, b_up)                                     # conv_up
         cat = torch.empty((B, H, W, half * len(scales)), device=x.device, dtype=x.dtype)
-        saved = []
-        for i, (s, w) in enumerate(zip(scales, dw_weights)):
-            k = w.shape[0]
-            out_slice = cat[..., i * half:(i + 1) * half]
-            if s != 1.:
-                pin = ops.pool_forward(t, (int(H * s), int(W * s)))
+        per_branch = {}
+        reduced = [i for i, s in enumerate(scales) if s != 1.]
+        full = [i for i, s in enumerate(scales) if s == 1.]
+        fork = _Fork(x.device, overlap_branches and bool(reduced) and bool(full), [t, cat])
+        with fork:
+            for i in reduced:
+                w = dw_weights[i]
+                k = w.shape[0]
+                pin = ops.pool_forward(t, (int(H * scales[i]), int(W * scales[i])))
                 c = ops.dwconv_forward(pin, w, None, 1, k // 2, 1)
-                ops.upsample_forward_into(ops.gate_forward(c, inv_scale), out_slice)
-                saved += [pin, c]
-            else:
-                c = ops.dwconv_forward(t, w, None, 1, k // 2, 1)
-                ops.gate_forward_into(c, out_slice, inv_scale)
-                saved += [c]
+                ops.upsample_forward_into(ops.gate_forward(c, inv_scale), cat[..., i * half:(i + 1) * half])
+                per_branch[i] = [pin, c]
+        for i in full:
+            w = dw_weights[i]
+            k = w.shape[0]
+            c = ops.dwconv_forward(t, w, None, 1, k // 2, 1)
+            ops.gate_forward_into(c, cat[..., i * half:(i + 1) * half], inv_scale)
+            per_branch[i] = [c]
+        fork.join([v for i in reduced for v in per_branch[i]])
+        saved = [v for i in range(len(scales)) for v in per_branch[i]]
         y = F.linear(cat, w_out, b_out)                                  # conv_out
         mean = x.mean(dim=(1, 2))                                        # [B, dim]
         ops.add_pooled_(y, F.linear(mean, w_pool, b_pool))               # + conv_pool(mean), broadcast
@@ -77,18 +139,20 @@ class ConvBlockFunction(torch.autograd.Function):
         dmean = dpooled.mm(w_pool)                                       # [B, dim]
 
         d_dw = [None] * n
-        dt = None
-        order = sorted(range(n), key=lambda i: scales[i] != 1.)          # a full-resolution branch first
         pos = {}
         off = 0
         for i, s in enumerate(scales):
             pos[i] = off
             off += 2 if s != 1. else 1
-        for i in order:
-            s, w = scales[i], dw_weights[i]
+        reduced = [i for i, s in enumerate(scales) if s != 1.]
+        full = [i for i, s in enumerate(scales) if s == 1.]
+
+        def branch_backward(i):
+            """dW of branch i (stored in d_dw) and the gradient w.r.t. the branch's conv input."""
+            w = dw_weights[i]
             k = w.shape[0]
             gslice = dcat[..., i * half:(i + 1) * half]
-            if s != 1.:
+            if scales[i] != 1.:
                 pin, c = saved[pos[i]], saved[pos[i] + 1]
                 dgate = ops.upsample_backward_from(gslice, (c.shape[1], c.shape[2]))
                 dc = ops.gate_backward(c, dgate, ctx.inv_scale)
@@ -98,14 +162,28 @@ class ConvBlockFunction(torch.autograd.Function):
             # parameter gradient first, then the input gradient (whoever reduces parameter gradients
             # across ranks can start earlier)
             d_dw[i], _ = ops.dwconv_backward_weight(pin, dc, k, 1, k // 2, 1)
-            dpin = ops.dwconv_backward_input(dc, w, (pin.shape[1], pin.shape[2]), 1, k // 2, 1)
-            if s != 1.:
-                if dt is None:
-                    dt = ops.pool_backward(dpin, (H, W))
-                else:
-                    ops.pool_backward_accumulate(dpin, dt)
+            return ops.dwconv_backward_input(dc, w, (pin.shape[1], pin.shape[2]), 1, k // 2, 1)
+
+        # reduced-resolution branches on the side stream, full-resolution ones on this stream
+        dpins = {}
+        fork = _Fork(x.device, overlap_branches and bool(reduced) and bool(full), [dcat] + saved)
+        with fork:
+            for i in reduced:
+                dpins[i] = branch_backward(i)
+        dt = None
+        for i in full:
+            dpin = branch_backward(i)
+            dt = dpin if dt is None else dt.add_(dpin)
+        fork.join([dpins[i] for i in reduced] + [d_dw[i] for i in reduced])
+        for i in reduced:
+            if dt is None:
+                dt = ops.pool_backward(dpins[i], (H, W))
             else:
-                dt = dpin if dt is None else dt.add_(dpin)
+                ops.pool_backward_accumulate(dpins[i], dt)
+
+        if early_gradient_hook is not None:
+            early = [(w_out, d_w_out), (w_pool, d_w_pool)] + list(zip(dw_weights, d_dw))
+            early_gradient_hook(early, dbias if (ctx.has_bias[1] or ctx.has_bias[2]) else None)
 
         dt2 = dt.view(N, -1)
         d_w_up = dt2.t().mm(x.view(N, dim))

@@ -229,6 +229,9 @@ inline bool plan_fwd_tile(int OH, int OW, int KH, int K, int esize, int wreg_byt
     if (force_th && force_tw) {
         consider(force_th, force_tw);
     } else {
+        // Widths that are multiples of 48 (48, 96, ...) split into three-strip tiles without a ragged
+        // column of tiles; measured 2-13 % faster than 32x32 there.
+        if (OW % 48 == 0) consider(16, 48);
         for (const TileShape& t : kTilePreference) consider(t.th, t.tw);
     }
     if (n == 0) return false;
@@ -236,7 +239,8 @@ inline bool plan_fwd_tile(int OH, int OW, int KH, int K, int esize, int wreg_byt
     for (int i = 0; i < n; ++i) {
         if (cands[i].eff < 0.97 * best_eff) continue;
         if (most < 0 || cands[i].blocks > cands[most].blocks) most = i;
-        if (cands[i].blocks >= 3.0 * (cands[i].two ? 2 : 1) * sms) { pick = i; break; }
+        const double want = (cands[i].tw == 48 ? 2.0 : 3.0) * (cands[i].two ? 2 : 1) * sms;
+        if (cands[i].blocks >= want) { pick = i; break; }
     }
     if (pick < 0) pick = most;
     const Cand& c = cands[pick];

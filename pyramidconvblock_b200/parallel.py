@@ -26,10 +26,14 @@ class GradientBucket:
         dev = self.params[0].device
         self.flat = torch.zeros(self.numel, dtype=dtype, device=dev)
         self.views = []
+        self.offsets = []
         off = 0
         for p, n in zip(self.params, self.sizes):
             self.views.append(self.flat[off:off + n].view(p.shape))
+            self.offsets.append(off)
             off += n
+        self._early_work = None
+        self._early_start = None
 
     def pack(self):
         """Copy (and up-cast) the current ``.grad`` of every parameter into the flat buffer."""
@@ -53,13 +57,62 @@ class GradientBucket:
             if p.grad is None:
                 p.grad = v.to(p.dtype).clone()
 
+    def _distributed(self):
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+
     def allreduce(self):
-        """pack -> all_reduce(SUM) -> unpack.  A no-op reduction when there is one rank."""
-        self.pack()
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+        """pack -> all_reduce(SUM) -> unpack.  A no-op reduction when there is one rank.
+
+        If ``reduce_early`` already sent a tail of the bucket during backward, only the head that
+        was not ready then is reduced now."""
+        work, start = self._early_work, self._early_start
+        self._early_work, self._early_start = None, None
+        if work is None:
+            self.pack()
+            if self._distributed():
+                dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            head = [(v, p.grad) for p, v, o in zip(self.params, self.views, self.offsets) if o < start]
+            for v, g in head:
+                if g is None:
+                    v.zero_()
+            head = [(v, g) for v, g in head if g is not None]
+            if head:
+                torch._foreach_copy_([v for v, _ in head], [g for _, g in head])
+            if start > 0:
+                dist.all_reduce(self.flat[:start], op=dist.ReduceOp.SUM, group=self.group)
+            work.wait()
         self.unpack()
         return self.flat
+
+    def reduce_early(self, grads, shared_bias_grad=None):
+        """Called from inside backward with [(parameter, gradient), ...] that are already final.  If
+        they cover a whole tail of the bucket, that tail is packed and its all-reduce started at once
+        (asynchronously, on the communication stream) while backward goes on; ``allreduce()`` later
+        handles the rest.  Anything else is left for ``allreduce()``.  ``shared_bias_grad`` stands for
+        every 1-D parameter of the tail that is not listed (the two output biases share one gradient)."""
+        if not self._distributed() or self._early_work is not None:
+            return
+        by_ptr = {p.data_ptr(): i for i, p in enumerate(self.params)}
+        got = {}
+        for p, g in grads:
+            i = by_ptr.get(p.data_ptr())
+            if i is not None and g is not None:
+                got[i] = g
+        if not got:
+            return
+        first = min(got)
+        for i in range(first, len(self.params)):
+            if i not in got:
+                if shared_bias_grad is not None and self.params[i].dim() == 1:
+                    got[i] = shared_bias_grad
+                else:
+                    return   # not a complete tail
+        idx = list(range(first, len(self.params)))
+        torch._foreach_copy_([self.views[i] for i in idx], [got[i] for i in idx])
+        self._early_start = self.offsets[first]
+        self._early_work = dist.all_reduce(self.flat[self._early_start:], op=dist.ReduceOp.SUM, group=self.group,
+                                           async_op=True)
 
 
 def shard_batch(global_batch, rank, world_size):
@@ -73,11 +126,16 @@ def shard_batch(global_batch, rank, world_size):
 def train_step(model, bucket, x, grad_out):
     """One data-parallel step on this rank's shard: forward, backward with the given upstream
     gradient, gradient all-reduce.  Returns (y, dX); parameter gradients are left in ``.grad``."""
+    from . import block_function
     for p in bucket.params:
         p.grad = None
     if x.requires_grad:
         x.grad = None
     y = model(x)
-    y.backward(grad_out)
+    block_function.early_gradient_hook = bucket.reduce_early
+    try:
+        y.backward(grad_out)
+    finally:
+        block_function.early_gradient_hook = None
     bucket.allreduce()
     return y, x.grad

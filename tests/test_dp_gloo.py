@@ -62,6 +62,20 @@ def _worker(rank, world, port, ret):
         ok = all(torch.allclose(a, p.grad, rtol=1e-4, atol=1e-5) for a, p in zip(reduced, full.parameters()))
         ok = ok and torch.allclose(dx, xf.grad[lo:hi], rtol=1e-4, atol=1e-6)
         ok = ok and bucket.numel == sum(p.numel() for p in model.parameters())
+        # the overlapped form: a tail of the bucket is reduced "during backward" (reduce_early), the
+        # head afterwards; the result must equal the one-shot reduction above
+        model2 = OracleBlock(16, 5)
+        xs2 = x[lo:hi].clone().requires_grad_(True)
+        model2(xs2).backward(go[lo:hi])
+        bucket2 = GradientBucket(model2.parameters())
+        params2 = list(model2.parameters())
+        bucket2.reduce_early([(p, p.grad) for p in params2[1:] if p.dim() > 1], shared_bias_grad=params2[-1].grad)
+        started = bucket2._early_work is not None
+        bucket2.allreduce()
+        ok = ok and started and all(torch.allclose(p.grad, r, rtol=1e-4, atol=1e-4) for p, r in zip(params2, reduced))
+        # an incomplete tail must be left to allreduce()
+        bucket2.reduce_early([(params2[2], params2[2].grad)])
+        ok = ok and bucket2._early_work is None
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
