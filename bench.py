@@ -14,8 +14,8 @@ Prints ONE JSON line (rank 0).  ``value`` is images/s of the whole job with inpu
 HBM; ``e2e`` is the same metric through the public module API with the step's inputs copied
 from pinned host memory and the reduced gradients read back every step.  ``roofline`` covers the
 dominant kernel (the TMA-tiled depthwise convolution, which runs forward and input-gradient),
-timed live with CUDA events inside the timed region; ``kernels`` lists every C-ABI entry point
-the same way.  ``cpu_baseline`` is the reference's CPU path (torch ``F.conv2d(groups=C)`` +
+timed with CUDA events around every launch in a second pass over the same steps (see the comment
+there); ``kernels`` lists every C-ABI entry point the same way.  ``cpu_baseline`` is the reference's CPU path (torch ``F.conv2d(groups=C)`` +
 ``adaptive_avg_pool2d`` + bilinear ``interpolate`` composition, from ``oracle/``) timed on the
 host cores on a bounded sample.  ``--impl reference`` times only that CPU path.
 """
@@ -376,6 +376,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the k=9/13/17 side sweeps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="do not capture the step into a CUDA graph")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -400,7 +401,7 @@ def main():
 
     from pyramid_dwconv import ConvBlock
     from pyramidconvblock_b200 import check_device_status, ops
-    from pyramidconvblock_b200.parallel import GradientBucket, shard_batch, train_step
+    from pyramidconvblock_b200.parallel import GradientBucket, GraphedTrainStep, shard_batch, train_step
 
     lo, hi = shard_batch(GLOBAL_BATCH, rank, world)
     local_b = hi - lo
@@ -424,25 +425,51 @@ def main():
         return float(t.item())
 
     # ---- device-resident arm ----------------------------------------------------------------------
+    # The step (forward, backward, gradient all-reduce) is captured once into a CUDA graph and replayed;
+    # --no-graph keeps the eager launches.
+    step = None
+    if not args.no_graph:
+        step = GraphedTrainStep(model, bucket, x, gout)
+        if not step.graphed and rank == 0:
+            print("note: CUDA graph capture failed (%s); running eagerly" % getattr(step, "error", "?"), file=sys.stderr)
+    graphed = step is not None and step.graphed
+
+    def run_step():
+        if graphed:
+            step()
+        else:
+            train_step(model, bucket, x, gout)
+
     for _ in range(args.warmup):
-        train_step(model, bucket, x, gout)
+        run_step()
     barrier()
     sampler = ClockSampler(physical_gpu_index(local_rank))
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ops.KernelTimer() as timer:
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            train_step(model, bucket, x, gout)
-        e1.record()
-        barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_per_step * 1e-3)
     check_device_status(device)
+
+    # Per-launch durations: the same steps again with CUDA events around every C-ABI call.  The two
+    # branches of the block normally run on two streams and overlap, which would smear one kernel's
+    # duration over another's; for this pass they are put back on one stream so that each figure is
+    # that kernel alone on the GPU.  (The clock sampler stays on over both passes.)
+    from pyramidconvblock_b200 import block_function
+    block_function.overlap_branches = False
+    with ops.KernelTimer() as timer:
+        for _ in range(args.steps):
+            train_step(model, bucket, x, gout)
+        barrier()
+    block_function.overlap_branches = True
+    clocks = sampler.stop() if rank == 0 else None
     summary = timer.summary()
     launches = timer.kernel_launches()
 
@@ -450,14 +477,20 @@ def main():
     x_host = x.detach().cpu().pin_memory()
     g_host = gout.cpu().pin_memory()
     grads_host = torch.empty(bucket.numel, dtype=torch.float32).pin_memory()
-    x_dev = torch.empty_like(x_host, device=device)
-    g_dev = torch.empty_like(g_host, device=device)
+    x_dev = None if graphed else torch.empty_like(x_host, device=device)
+    g_dev = None if graphed else torch.empty_like(g_host, device=device)
 
     def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        g_dev.copy_(g_host, non_blocking=True)
-        xin = x_dev.detach().requires_grad_(True)
-        train_step(model, bucket, xin, g_dev)
+        if graphed:
+            with torch.no_grad():
+                x.copy_(x_host, non_blocking=True)      # the graph's static input buffers
+                gout.copy_(g_host, non_blocking=True)
+            step()
+        else:
+            x_dev.copy_(x_host, non_blocking=True)
+            g_dev.copy_(g_host, non_blocking=True)
+            xin = x_dev.detach().requires_grad_(True)
+            train_step(model, bucket, xin, g_dev)
         grads_host.copy_(bucket.flat, non_blocking=True)
         torch.cuda.current_stream(device).synchronize()   # the caller holds the result on the host
 
@@ -474,9 +507,24 @@ def main():
     h2d = x_host.numel() * x_host.element_size() + g_host.numel() * g_host.element_size()
     d2h = grads_host.numel() * grads_host.element_size()
 
-    if rank != 0:
+    def leave():
+        """End of the run for a rank of a multi-process job.  A captured graph holds NCCL work, and
+        tearing the communicator down under it can block; so: drop the graph, drain the device, meet
+        the other ranks once more, flush, and end the process without running the NCCL destructors."""
+        nonlocal step
         if world > 1:
-            dist.destroy_process_group()
+            if step is not None and step.graph is not None:
+                step.graph.reset()
+            step = None
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            torch.cuda.synchronize(device)
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        leave()
         return
 
     # ---- roofline of the dominant kernel and per-entry-point table ---------------------------------
@@ -522,6 +570,9 @@ def main():
         "peak_source": "148 SMs x 128 FP32 lanes x 2 x sm_max_mhz of MEASURED_PEAKS.json (%s); tensor cores do not "
                        "apply to a depthwise convolution" % peaks["source"],
         "flops_per_launch": dom_flops, "avg_launch_ms": round(dom_ms, 4), "launches": dom_calls,
+        "timing": "CUDA events around each launch over the same %d steps repeated with the block's two branches on "
+                  "one stream (kernel alone on the GPU); the timed region of `value` overlaps them on two streams"
+                  % args.steps,
         "hbm_bytes_per_launch": 2 * local_b * HEIGHT * WIDTH * half * es,
         "hbm_time_at_peak_ms": round(2 * local_b * HEIGHT * WIDTH * half * es / (peaks["hbm_gbs"] * 1e9) * 1e3, 4),
         "traffic": traffic_per_image * local_b if traffic_per_image else None,
@@ -536,7 +587,7 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": local_b,
-                   "parallelism": "dp%d" % world,
+                   "parallelism": "dp%d" % world, "cuda_graph": graphed,
                    "l2": "inputs larger than L2 (x and grad of %d MB each per GPU)" % (x.numel() * 2 // 2 ** 20)},
         "e2e": {"value": round(GLOBAL_BATCH / (e2e_ms * 1e-3), 2), "unit": "images/s", "ms_per_step": round(e2e_ms, 4),
                 "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -552,8 +603,7 @@ def main():
         result["extra"] = extra_sweeps(device)
         result["extra"]["reference_triton_same_gpu"] = reference_triton_timings(device)
     print(json.dumps(result))
-    if world > 1:
-        dist.destroy_process_group()
+    leave()
 
 
 # DRAM bytes (read + write) of one dwconv_tiled_kernel launch per image of [96,96,256] bf16, k=17,

@@ -139,3 +139,55 @@ def train_step(model, bucket, x, grad_out):
         block_function.early_gradient_hook = None
     bucket.allreduce()
     return y, x.grad
+
+
+class GraphedTrainStep:
+    """``train_step`` captured once into a CUDA graph and replayed.
+
+    A step is ~60 kernel launches plus the gradient all-reduce; with a small per-GPU batch (and eight
+    ranks sharing one host's cores) enqueueing them costs more CPU time than the GPU needs to run
+    them.  Replaying a captured graph makes the step one launch.  ``x`` and ``grad_out`` given at
+    construction are the static input buffers: copy new data into them (``copy_``) before each call.
+    After a call, ``y``, ``x.grad`` and every parameter's ``.grad`` (already reduced over the ranks)
+    hold the step's results, in the same memory every time.
+
+    If capture is not possible (for instance a collective that cannot be captured), the object falls
+    back to calling ``train_step`` eagerly; ``graphed`` tells which.
+    """
+
+    def __init__(self, model, bucket, x, grad_out, warmup=3):
+        self.model, self.bucket, self.x, self.grad_out = model, bucket, x, grad_out
+        self.graph = None
+        self.y = None
+        self.graphed = False
+        device = x.device
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                train_step(model, bucket, x, grad_out)
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.y, _ = train_step(model, bucket, x, grad_out)
+            self.graph = graph
+            self.graphed = True
+            # the tensors the graph writes its results to
+            self.param_grads = [p.grad for p in bucket.params]
+            self.dx = x.grad
+        except Exception as e:   # leave a usable eager path behind
+            self.error = str(e).splitlines()[0] if str(e) else type(e).__name__
+            torch.cuda.synchronize(device)
+            self.y, _ = train_step(model, bucket, x, grad_out)
+
+    def __call__(self):
+        if self.graphed:
+            self.graph.replay()
+            for p, g in zip(self.bucket.params, self.param_grads):
+                p.grad = g
+            self.x.grad = self.dx
+        else:
+            self.y, _ = train_step(self.model, self.bucket, self.x, self.grad_out)
+        return self.y, self.x.grad
