@@ -557,9 +557,15 @@ def main():
             fl = 2 * conv_fmas(b, h, w, c, k)
             entry["tflops"] = round(fl / (avg_ms * 1e-3) / 1e12, 3)
             entry["frac_fp32_peak"] = round(entry["tflops"] / peaks["fp32_tflops"], 4)
-        elif label in ("pool_fwd", "pool_bwd", "upsample_fwd", "upsample_bwd"):
+        elif label in ("pool_fwd", "pool_bwd", "pool_bwd_accumulate", "upsample_fwd", "upsample_bwd"):
             b, h, w, c, oh, ow = shape
-            byts = b * c * es * (h * w + oh * ow)
+            # the accumulating form reads and rewrites its target
+            byts = b * c * es * ((2 if label == "pool_bwd_accumulate" else 1) * h * w + oh * ow)
+            entry["gbs"] = round(byts / (avg_ms * 1e-3) / 1e9, 1)
+            entry["frac_hbm_peak"] = round(entry["gbs"] / peaks["hbm_gbs"], 4)
+        elif label == "add_pooled":
+            b, pixels, c = shape
+            byts = 2 * b * pixels * c * es
             entry["gbs"] = round(byts / (avg_ms * 1e-3) / 1e9, 1)
             entry["frac_hbm_peak"] = round(entry["gbs"] / peaks["hbm_gbs"], 4)
         elif label in ("gate_fwd", "gate_bwd"):

@@ -339,7 +339,7 @@ def pool_backward_accumulate(grad_out, dx):
     B, OH, OW, C = grad_out.shape
     H, W = dx.shape[1], dx.shape[2]
     with torch.cuda.device(dx.device):
-        rc = _call("pool_bwd", (B, H, W, C, OH, OW), 1, dx.device, lambda: _lib.lib().pdw_pool_bwd_accumulate(
+        rc = _call("pool_bwd_accumulate", (B, H, W, C, OH, OW), 1, dx.device, lambda: _lib.lib().pdw_pool_bwd_accumulate(
             _ptr(grad_out), _ptr(dx), B, H, W, C, OH, OW, _dtype_code(dx), _stream(dx)))
     _lib.check(rc, "pdw_pool_bwd_accumulate")
     return dx

@@ -9,6 +9,8 @@ message on NVLink/NVSwitch.  The reference has no distributed code; this module 
 The bucket logic is plain ``torch.distributed`` and therefore also runs over ``gloo`` on CPU
 tensors, which is how it is tested without GPUs.
 """
+import warnings
+
 import torch
 import torch.distributed as dist
 
@@ -170,8 +172,12 @@ class GraphedTrainStep:
         torch.cuda.synchronize(device)
         try:
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self.y, _ = train_step(model, bucket, x, grad_out)
+            # (warm-up and capture run on different non-default streams; autograd's notice about the
+            # gradient accumulators having been created on another stream does not apply to a capture)
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore", UserWarning)
+                with torch.cuda.graph(graph):
+                    self.y, _ = train_step(model, bucket, x, grad_out)
             self.graph = graph
             self.graphed = True
             # the tensors the graph writes its results to
