@@ -12,7 +12,7 @@ thread_local int g_last_cuda_error = 0;
 // ---------------------------------------------------------------------------------------------
 // Library-wide helpers
 // ---------------------------------------------------------------------------------------------
-static int g_tuning[7] = {1, 16, 0, 0, 0, 0, 0};
+static int g_tuning[8] = {1, 16, 0, 0, 0, 0, 0, 0};
 int tuning(int key) { return g_tuning[key]; }
 
 int sm_count() {
@@ -270,7 +270,7 @@ const char* pdw_status_string(int status) {
 int pdw_last_cuda_error(void) { return g_last_cuda_error; }
 
 int pdw_set_tuning(int key, int value) {
-    if (key < 0 || key > 6) return -1;
+    if (key < 0 || key > 7) return -1;
     if (key == 1 && value != 16 && value != 32) return -1;
     const int prev = g_tuning[key];
     g_tuning[key] = value;

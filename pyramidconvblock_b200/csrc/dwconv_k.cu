@@ -1,6 +1,6 @@
 // Instantiates the tiled depthwise-convolution kernels for ONE filter width.
 // Compiled once per supported width with -DPDW_K=<K> so that the widths build in parallel.
-#include "dwconv_tiled.cuh"
+#include "dwconv_stream.cuh"
 
 #ifndef PDW_K
 #error "compile with -DPDW_K=<filter width>"
@@ -15,6 +15,10 @@ template <typename T>
 static int tiled_for_type(const TiledArgs& a) {
     const int ct = tuning(1);
     if constexpr (sizeof(T) == 2) {
+        if (tuning(0) && ct == 16 && tuning(7) && aligned_to(a.w, 16)) {
+            const int rc = launch_stream<T, PDW_K>(a);
+            if (rc != PDW_ERR_UNSUPPORTED) return rc;
+        }
         if (tuning(0)) return ct == 32 ? launch_tiled<T, PDW_K, 32, 1>(a) : launch_tiled<T, PDW_K, 16, 1>(a);
     }
     return ct == 32 ? launch_tiled<T, PDW_K, 32, 0>(a) : launch_tiled<T, PDW_K, 16, 0>(a);

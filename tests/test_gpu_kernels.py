@@ -31,7 +31,7 @@ def rounded(t, dtype):
 @pytest.fixture(autouse=True)
 def _reset_tuning_and_check_status():
     L = _lib.lib()
-    defaults = ((0, 1), (1, 16), (2, 0))
+    defaults = ((0, 1), (1, 16), (2, 0), (7, 0))
     for key, value in defaults:
         L.pdw_set_tuning(key, value)
     yield
@@ -125,6 +125,16 @@ def test_dwconv_general_geometry(geom, dtype):
     C = geom.get("C", 8)
     run_conv_case(2, 17, 15, C, geom["k"], dtype, seed=500, stride=geom["stride"], padding=geom["padding"],
                   dilation=geom["dilation"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k", [3, 9, 13, 17])
+def test_dwconv_streaming_variant(k, dtype):
+    """The persistent warp-specialised form of the 16-bit forward / input-gradient kernel (tuning key 7)
+    against the oracle, on a shape with ragged tiles and a partial channel tile."""
+    _lib.lib().pdw_set_tuning(7, 1)
+    run_conv_case(2, 45, 52, 24, k, dtype, seed=650 + k)
+    run_conv_case(1, 20, 23, 16, k, dtype, seed=660 + k, padding=(1, k - 1))
 
 
 def test_dwconv_untiled_kernels_agree_with_tiled():
