@@ -105,3 +105,44 @@ def test_bucket_roundtrip_single_process():
     assert b.flat.dtype == torch.float32 and b.numel == 8
     assert torch.equal(lin.weight.grad, torch.ones_like(lin.weight))
     assert torch.equal(lin.bias.grad, torch.zeros_like(lin.bias))
+
+
+def _lonely_worker(rank, world, port, ret):
+    """Rank 1 leaves between steps (after a first good reduction) and never joins the second one; rank 0
+    must get an error from its next all-reduce within the process group's short timeout, not hang."""
+    import datetime
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from pyramidconvblock_b200.parallel import GradientBucket
+    lin = torch.nn.Linear(4, 3)
+    lin.weight.grad = torch.full_like(lin.weight, float(rank + 1))
+    lin.bias.grad = torch.zeros_like(lin.bias)
+    bucket = GradientBucket(lin.parameters())
+    bucket.allreduce()
+    first_ok = bool(torch.equal(lin.weight.grad, torch.full_like(lin.weight, 3.0)))
+    if rank == 1:
+        ret[rank] = first_ok
+        os._exit(0)        # gone: no second step
+    try:
+        bucket.allreduce()
+        ret[rank] = False  # a reduction with a missing rank must not "succeed"
+    except Exception:
+        ret[rank] = first_ok
+    os._exit(0)
+
+
+def test_missing_rank_is_reported_not_waited_for():
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        ctx = mp.get_context("spawn")
+        port = _free_port()
+        procs = [ctx.Process(target=_lonely_worker, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=60)
+            assert not p.is_alive(), "a rank hung"
+        assert dict(ret) == {0: True, 1: True}
