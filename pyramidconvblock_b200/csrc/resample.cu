@@ -188,6 +188,79 @@ __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restri
     }
 }
 
+// Table variant used whenever the tables fit: a thread keeps one channel vector and walks a contiguous
+// run of input columns.  Where an input pixel lies in exactly one pooling window (every case with
+// in % out == 0, e.g. the 2x pooling of ConvBlock) neighbouring input columns share that window's
+// gradient: it is loaded, scaled and packed once and then only stored, so the sweep is almost pure
+// 16-byte stores (plus the read-modify-write of the accumulating form).
+template <typename T, int V>
+__global__ void __launch_bounds__(kRowThreads) pool_bwd_seg_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
+                                                                   const bool accumulate) {
+    extern __shared__ int itab[];     // [W] first output column, [W] count, float [OW] 1/width, float [16] 1/height
+    float* inv_kw = reinterpret_cast<float*>(itab + 2 * s.W);
+    float* inv_kh = inv_kw + s.OW;
+    const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
+    const int cv = s.C / V;
+    const int oh0 = win_start(ih, s.OH, s.H), noh = win_end(ih, s.OH, s.H) - oh0;
+    for (int iw = threadIdx.x; iw < s.W; iw += kRowThreads) {
+        const int o0 = win_start(iw, s.OW, s.W);
+        itab[iw] = o0;
+        itab[s.W + iw] = win_end(iw, s.OW, s.W) - o0;
+    }
+    for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads)
+        inv_kw[ow] = 1.f / (float)(win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW));
+    if ((int)threadIdx.x < noh && threadIdx.x < kMaxPoolRows)
+        inv_kh[threadIdx.x] = 1.f / (float)(win_end(oh0 + threadIdx.x, s.H, s.OH) - win_start(oh0 + threadIdx.x, s.H, s.OH));
+    __syncthreads();
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
+    const int seg = (s.W + rt.lanes - 1) / rt.lanes;
+    const int iw_begin = rt.lane * seg, iw_end = min(s.W, iw_begin + seg);
+    T* drow = dx + ((size_t)b * s.H + ih) * s.W * s.C;
+    const T* grow = go + ((size_t)b * s.OH + oh0) * s.OW * s.C;
+    const int row_stride = s.OW * s.C;
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        const int c = vec * V;
+        int cached = -1;            // output column whose scaled gradient is in val / packed
+        float val[V];
+        Vec<T, V> packed;
+        for (int iw = iw_begin; iw < iw_end; ++iw) {
+            const int ow0 = itab[iw], now = itab[s.W + iw];
+            T* d = drow + iw * s.C + c;
+            if (noh == 1 && now == 1) {
+                if (ow0 != cached) {
+                    cached = ow0;
+                    const Vec<T, V> g = ldv<T, V>(grow + ow0 * s.C + c);
+                    const float w = inv_kh[0] * inv_kw[ow0];
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        val[i] = Elem<T>::to_f(g.v[i]) * w;
+                        packed.v[i] = Elem<T>::from_f(val[i]);
+                    }
+                }
+                if (accumulate) {
+                    const Vec<T, V> old = ldv<T, V>(d);
+                    Vec<T, V> r;
+#pragma unroll
+                    for (int i = 0; i < V; ++i) r.v[i] = Elem<T>::from_f(val[i] + Elem<T>::to_f(old.v[i]));
+                    *reinterpret_cast<Vec<T, V>*>(d) = r;
+                } else {
+                    *reinterpret_cast<Vec<T, V>*>(d) = packed;
+                }
+            } else {
+                float acc[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = 0.f;
+                const T* p = grow + ow0 * s.C + c;
+                for (int j = 0; j < noh; ++j, p += row_stride)
+                    for (int k = 0; k < now; ++k) fma_vec<T, V>(acc, ldv<T, V>(p + k * s.C), inv_kh[j] * inv_kw[ow0 + k]);
+                if (accumulate) fma_vec<T, V>(acc, ldv<T, V>(d), 1.f);
+                store_vec<T, V>(d, acc);
+            }
+        }
+    }
+}
+
 // ---- bilinear resize (align_corners = False) ---------------------------------------------------
 struct Tap { int i0, i1; float l0, l1; };
 __device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
@@ -251,6 +324,65 @@ __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __re
                 fma_vec<T, V>(acc, b11, ty.l1 * tb.l1);
                 store_vec<T, V>(yrow + ow2 * s.ld + c, acc);
             }
+        }
+    }
+}
+
+// Table variant used whenever the table fits: a thread keeps one channel vector and walks a contiguous
+// run of destination columns.  The two source columns of the current destination column are held in
+// registers already combined over the two source rows (the row weights are the same for the whole
+// block); when the walk reaches the next source column only that one is fetched.  With an upsampling
+// ratio r every source vector is thus loaded and converted once per r destination columns.
+template <typename T, int V>
+__global__ void __launch_bounds__(kRowThreads) upsample_fwd_seg_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s,
+                                                                       float scale_h, float scale_w) {
+    extern __shared__ int itab[];                 // [OW] x {i0, i1, l0, l1}
+    Tap* xt = reinterpret_cast<Tap*>(itab);
+    const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
+    const int cv = s.C / V;
+    for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads) xt[ow] = source_taps(ow, scale_w, s.W);
+    __syncthreads();
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
+    const Tap ty = source_taps(oh, scale_h, s.H);
+    const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C;
+    const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C;
+    T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.ld;
+    const int seg = (s.OW + rt.lanes - 1) / rt.lanes;
+    const int ow_begin = rt.lane * seg, ow_end = min(s.OW, ow_begin + seg);
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        const int c = vec * V;
+        int c0 = -1, c1 = -1;          // source columns held in v0 / v1
+        float v0[V], v1[V];
+        auto fetch = [&](int i, float (&v)[V]) {
+            const Vec<T, V> a = ldv<T, V>(r0 + i * s.C + c), bb = ldv<T, V>(r1 + i * s.C + c);
+#pragma unroll
+            for (int q = 0; q < V; ++q) v[q] = ty.l0 * Elem<T>::to_f(a.v[q]) + ty.l1 * Elem<T>::to_f(bb.v[q]);
+        };
+        for (int ow = ow_begin; ow < ow_end; ++ow) {
+            const Tap t = xt[ow];
+            if (t.i0 != c0) {
+                if (t.i0 == c1) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) v0[q] = v1[q];
+                } else {
+                    fetch(t.i0, v0);
+                }
+                c0 = t.i0;
+            }
+            if (t.i1 != c1) {
+                if (t.i1 == c0) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) v1[q] = v0[q];
+                } else {
+                    fetch(t.i1, v1);
+                }
+                c1 = t.i1;
+            }
+            float acc[V];
+#pragma unroll
+            for (int q = 0; q < V; ++q) acc[q] = t.l0 * v0[q] + t.l1 * v1[q];
+            store_vec<T, V>(yrow + ow * s.ld + c, acc);
         }
     }
 }
@@ -494,11 +626,11 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
             else pool_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s);
         } else if constexpr (OP == Resample::PoolBwd) {
             const size_t tab = sizeof(int) * (2 * (size_t)W + (size_t)OW + kMaxPoolRows);
-            if (tab <= kTableMax && (OH + H - 1) / H + 1 <= kMaxPoolRows) pool_bwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
+            if (tab <= kTableMax && (OH + H - 1) / H + 1 <= kMaxPoolRows) pool_bwd_seg_kernel<T, V><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
             else pool_bwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
         } else if constexpr (OP == Resample::UpFwd) {
             const size_t tab = sizeof(Tap) * (size_t)OW;
-            if (tab <= kTableMax) upsample_fwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s, sh, sw);
+            if (tab <= kTableMax) upsample_fwd_seg_kernel<T, V><<<blocks, kRowThreads, tab, st>>>(in, out, s, sh, sw);
             else upsample_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
         } else {
             const size_t table = sizeof(float) * (kMaxTaps + 2 + 2 * (size_t)W + (size_t)W * kMaxTaps);
