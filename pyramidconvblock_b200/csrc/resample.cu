@@ -60,20 +60,7 @@ __device__ __forceinline__ void fma_vec(float (&acc)[V], const Vec<T, V>& d, flo
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = fmaf(Elem<T>::to_f(d.v[i]), w, acc[i]);
 }
-// acc += sum_{k<n} w * p[k*stride], loads issued four at a time so that several are in flight.
-template <typename T, int V>
-__device__ __forceinline__ void acc_run(float (&acc)[V], const T* p, int stride, int n, float w) {
-    for (int k0 = 0; k0 < n; k0 += 4) {
-        Vec<T, V> d[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (k0 + u < n) d[u] = ldv<T, V>(p + (k0 + u) * stride);
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (k0 + u < n) fma_vec<T, V>(acc, d[u], w);
-    }
-}
-// Same with one weight per element of the run: w[k] * wscale.
+// acc += sum_{k<n} (w[k] * wscale) * p[k*stride], loads issued four at a time so that several are in flight.
 template <typename T, int V>
 __device__ __forceinline__ void acc_run_weighted(float (&acc)[V], const T* p, int stride, int n, const float* w,
                                                  float wscale) {
@@ -142,45 +129,27 @@ __global__ void __launch_bounds__(kRowThreads) pool_fwd_kernel(const T* __restri
 
 // dx[ih,iw] = sum over the outputs whose window holds (ih,iw) of grad_out / window area.  The
 // outputs that hold input index i are exactly [floor(i*out/in), ceil((i+1)*out/in)).
+// This form computes every window on the fly; it serves extents whose tables do not fit shared memory.
 constexpr int kMaxPoolRows = 16;     // output rows that can hold one input row, for the table variant
-template <typename T, int V, bool TAB>
+template <typename T, int V>
 __global__ void __launch_bounds__(kRowThreads) pool_bwd_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
                                                                const bool accumulate) {
-    extern __shared__ int itab[];     // [W] first output column, [W] count, float [OW] 1/width, float [16] 1/height
-    float* inv_kw = reinterpret_cast<float*>(itab + 2 * s.W);
-    float* inv_kh_tab = inv_kw + s.OW;
     const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
     const int cv = s.C / V;
     const int oh0 = win_start(ih, s.OH, s.H), oh1 = win_end(ih, s.OH, s.H);
-    if (TAB) {
-        for (int iw = threadIdx.x; iw < s.W; iw += kRowThreads) {
-            const int o0 = win_start(iw, s.OW, s.W);
-            itab[iw] = o0;
-            itab[s.W + iw] = win_end(iw, s.OW, s.W) - o0;
-        }
-        for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads)
-            inv_kw[ow] = 1.f / (float)(win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW));
-        if ((int)threadIdx.x < oh1 - oh0 && threadIdx.x < kMaxPoolRows)
-            inv_kh_tab[threadIdx.x] =
-                1.f / (float)(win_end(oh0 + threadIdx.x, s.H, s.OH) - win_start(oh0 + threadIdx.x, s.H, s.OH));
-        __syncthreads();
-    }
     T* drow = dx + ((size_t)b * s.H + ih) * s.W * s.C;
     for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.W; w.next()) {
         const int iw = w.col, c = w.vec * V;
-        const int ow0 = TAB ? itab[iw] : win_start(iw, s.OW, s.W);
-        const int now = TAB ? itab[s.W + iw] : win_end(iw, s.OW, s.W) - ow0;
+        const int ow0 = win_start(iw, s.OW, s.W), ow1 = win_end(iw, s.OW, s.W);
         float acc[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
         for (int oh = oh0; oh < oh1; ++oh) {
-            const float inv_kh = TAB ? inv_kh_tab[oh - oh0]
-                                     : 1.f / (float)(win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH));
-            const T* row = go + (((size_t)b * s.OH + oh) * s.OW + ow0) * s.C + c;
-            for (int j = 0; j < now; ++j) {
-                const float ikw = TAB ? inv_kw[ow0 + j]
-                                      : 1.f / (float)(win_end(ow0 + j, s.W, s.OW) - win_start(ow0 + j, s.W, s.OW));
-                load_acc<T, V>(row + (size_t)j * s.C, acc, inv_kh * ikw);
+            const float inv_kh = 1.f / (float)(win_end(oh, s.H, s.OH) - win_start(oh, s.H, s.OH));
+            const T* row = go + (((size_t)b * s.OH + oh) * s.OW) * s.C + c;
+            for (int ow = ow0; ow < ow1; ++ow) {
+                const float ikw = 1.f / (float)(win_end(ow, s.W, s.OW) - win_start(ow, s.W, s.OW));
+                load_acc<T, V>(row + (size_t)ow * s.C, acc, inv_kh * ikw);
             }
         }
         if (accumulate) load_acc<T, V>(drow + (size_t)iw * s.C + c, acc, 1.f);   // dx += ...
@@ -276,55 +245,28 @@ __device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
     return t;
 }
 
-// s.H,s.W: source extent (small), s.OH,s.OW: destination extent.  TAB: the two source columns and
-// weights of every destination column come from a shared-memory table built once per block.  Two
-// destination columns per step: eight independent 16-byte loads in flight per thread.
-template <typename T, int V, bool TAB>
+// s.H,s.W: source extent (small), s.OH,s.OW: destination extent.  Table-free form (taps computed per
+// access) for widths whose table does not fit shared memory.
+template <typename T, int V>
 __global__ void __launch_bounds__(kRowThreads) upsample_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s,
                                                                    float scale_h, float scale_w) {
-    extern __shared__ int itab[];                 // [OW] x {i0, i1, l0, l1}
-    Tap* xt = reinterpret_cast<Tap*>(itab);
     const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
     const int cv = s.C / V;
-    if (TAB) {
-        for (int ow = threadIdx.x; ow < s.OW; ow += kRowThreads) xt[ow] = source_taps(ow, scale_w, s.W);
-        __syncthreads();
-    }
-    const RowThread rt = row_thread(cv);
-    if (rt.lane >= rt.lanes) return;
     const Tap ty = source_taps(oh, scale_h, s.H);
     const T* r0 = x + (((size_t)b * s.H + ty.i0) * s.W) * s.C;
     const T* r1 = x + (((size_t)b * s.H + ty.i1) * s.W) * s.C;
     T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.ld;
-    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
-        const int c = vec * V;
-        for (int ow = rt.lane; ow < s.OW; ow += 2 * rt.lanes) {
-            const int ow2 = ow + rt.lanes;
-            const bool two = ow2 < s.OW;
-            const Tap ta = TAB ? xt[ow] : source_taps(ow, scale_w, s.W);
-            const Tap tb = two ? (TAB ? xt[ow2] : source_taps(ow2, scale_w, s.W)) : ta;
-            const Vec<T, V> a00 = ldv<T, V>(r0 + ta.i0 * s.C + c), a01 = ldv<T, V>(r0 + ta.i1 * s.C + c);
-            const Vec<T, V> a10 = ldv<T, V>(r1 + ta.i0 * s.C + c), a11 = ldv<T, V>(r1 + ta.i1 * s.C + c);
-            const Vec<T, V> b00 = ldv<T, V>(r0 + tb.i0 * s.C + c), b01 = ldv<T, V>(r0 + tb.i1 * s.C + c);
-            const Vec<T, V> b10 = ldv<T, V>(r1 + tb.i0 * s.C + c), b11 = ldv<T, V>(r1 + tb.i1 * s.C + c);
-            float acc[V];
+    for (RowWalker w(cv, threadIdx.x, kRowThreads); w.col < s.OW; w.next()) {
+        const int ow = w.col, c = w.vec * V;
+        const Tap tx = source_taps(ow, scale_w, s.W);
+        float acc[V];
 #pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] = 0.f;
-            fma_vec<T, V>(acc, a00, ty.l0 * ta.l0);
-            fma_vec<T, V>(acc, a01, ty.l0 * ta.l1);
-            fma_vec<T, V>(acc, a10, ty.l1 * ta.l0);
-            fma_vec<T, V>(acc, a11, ty.l1 * ta.l1);
-            store_vec<T, V>(yrow + ow * s.ld + c, acc);
-            if (two) {
-#pragma unroll
-                for (int i = 0; i < V; ++i) acc[i] = 0.f;
-                fma_vec<T, V>(acc, b00, ty.l0 * tb.l0);
-                fma_vec<T, V>(acc, b01, ty.l0 * tb.l1);
-                fma_vec<T, V>(acc, b10, ty.l1 * tb.l0);
-                fma_vec<T, V>(acc, b11, ty.l1 * tb.l1);
-                store_vec<T, V>(yrow + ow2 * s.ld + c, acc);
-            }
-        }
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        load_acc<T, V>(r0 + (size_t)tx.i0 * s.C + c, acc, ty.l0 * tx.l0);
+        load_acc<T, V>(r0 + (size_t)tx.i1 * s.C + c, acc, ty.l0 * tx.l1);
+        load_acc<T, V>(r1 + (size_t)tx.i0 * s.C + c, acc, ty.l1 * tx.l0);
+        load_acc<T, V>(r1 + (size_t)tx.i1 * s.C + c, acc, ty.l1 * tx.l1);
+        store_vec<T, V>(yrow + (size_t)ow * s.ld + c, acc);
     }
 }
 
@@ -627,11 +569,11 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
         } else if constexpr (OP == Resample::PoolBwd) {
             const size_t tab = sizeof(int) * (2 * (size_t)W + (size_t)OW + kMaxPoolRows);
             if (tab <= kTableMax && (OH + H - 1) / H + 1 <= kMaxPoolRows) pool_bwd_seg_kernel<T, V><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
-            else pool_bwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
+            else pool_bwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
         } else if constexpr (OP == Resample::UpFwd) {
             const size_t tab = sizeof(Tap) * (size_t)OW;
             if (tab <= kTableMax) upsample_fwd_seg_kernel<T, V><<<blocks, kRowThreads, tab, st>>>(in, out, s, sh, sw);
-            else upsample_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
+            else upsample_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
         } else {
             const size_t table = sizeof(float) * (kMaxTaps + 2 + 2 * (size_t)W + (size_t)W * kMaxTaps);
             if (max_taps_per_source(H, OH) <= kMaxTaps && max_taps_per_source(W, OW) <= kMaxTaps && table <= 40 * 1024) {

@@ -284,3 +284,15 @@ def test_slice_variants_and_accumulate(dtype):
     chk(yd.float().cpu().numpy(), ref.numpy(), "add_pooled")
     with pytest.raises(RuntimeError):
         ops.gate_forward_into(convd, buf[..., lo:lo + C].permute(0, 2, 1, 3), inv)
+
+
+def test_very_wide_rows_take_the_table_free_kernels():
+    """Rows too wide for the per-block shared-memory tables (thousands of columns) run the kernels that
+    compute windows / taps per access; same results."""
+    x, go = draw([(1, 2, 12000, 8), (1, 1, 6000, 8)], 1300)
+    assert_close_fp32(ops.pool_forward(x.cuda(), (1, 6000)).cpu().numpy(), oracle.c_pool_fwd(x.numpy(), (1, 6000)))
+    assert_close_fp32(ops.pool_backward(go.cuda(), (2, 12000)).cpu().numpy(), oracle.c_pool_bwd(go.numpy(), (2, 12000)))
+    xs, gbig = draw([(1, 2, 3000, 8), (1, 4, 6000, 8)], 1301)
+    assert_close_fp32(ops.upsample_forward(xs.cuda(), (4, 6000)).cpu().numpy(), oracle.c_upsample_fwd(xs.numpy(), (4, 6000)))
+    assert_close_fp32(ops.upsample_backward(gbig.cuda(), (2, 3000)).cpu().numpy(),
+                      oracle.c_upsample_bwd(gbig.numpy(), (2, 3000)))
