@@ -230,6 +230,93 @@ __global__ void __launch_bounds__(kRowThreads) pool_bwd_seg_kernel(const T* __re
     }
 }
 
+// Uniform pooling (H % OH == 0 and W % OW == 0, e.g. the 2x pooling of ConvBlock; the forward kernel is
+// instantiated for window widths 2, 4 and 8): every window is rh x rw, no tables are needed, and the loads of several outputs are issued together so that enough
+// of them are in flight to cover the memory latency.
+template <typename T, int V, int RW>
+__global__ void __launch_bounds__(kRowThreads) pool_fwd_uniform_kernel(const T* __restrict__ x, T* __restrict__ y, const Shape s) {
+    const int oh = blockIdx.x % s.OH, b = blockIdx.x / s.OH;
+    const int cv = s.C / V, rh = s.H / s.OH;
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
+    const T* xin = x + ((size_t)b * s.H + oh * rh) * s.W * s.C;
+    T* yrow = y + ((size_t)b * s.OH + oh) * s.OW * s.C;
+    const int row_stride = s.W * s.C;
+    const float inv = 1.f / (float)(rh * RW);
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        const int c = vec * V;
+        for (int ow = rt.lane; ow < s.OW; ow += 2 * rt.lanes) {
+            const int ow2 = ow + rt.lanes;
+            const bool two = ow2 < s.OW;
+            float a0[V], a1[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) { a0[i] = 0.f; a1[i] = 0.f; }
+            const T* p0 = xin + ow * RW * s.C + c;
+            const T* p1 = xin + (two ? ow2 : ow) * RW * s.C + c;
+            for (int r = 0; r < rh; ++r, p0 += row_stride, p1 += row_stride) {
+                Vec<T, V> d0[RW], d1[RW];
+#pragma unroll
+                for (int u = 0; u < RW; ++u) {
+                    d0[u] = ldv<T, V>(p0 + u * s.C);
+                    d1[u] = ldv<T, V>(p1 + u * s.C);
+                }
+#pragma unroll
+                for (int u = 0; u < RW; ++u) {
+                    fma_vec<T, V>(a0, d0[u], inv);
+                    fma_vec<T, V>(a1, d1[u], inv);
+                }
+            }
+            store_vec<T, V>(yrow + ow * s.C + c, a0);
+            if (two) store_vec<T, V>(yrow + ow2 * s.C + c, a1);
+        }
+    }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kRowThreads) pool_bwd_uniform_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
+                                                                       const bool accumulate) {
+    const int ih = blockIdx.x % s.H, b = blockIdx.x / s.H;
+    const int cv = s.C / V, rh = s.H / s.OH, rw = s.W / s.OW;
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
+    const T* grow = go + ((size_t)b * s.OH + ih / rh) * s.OW * s.C;
+    T* drow = dx + ((size_t)b * s.H + ih) * s.W * s.C;
+    const float inv = 1.f / (float)(rh * rw);
+    constexpr int U = 4;     // gradient vectors fetched together
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        const int c = vec * V;
+        for (int ow = rt.lane; ow < s.OW; ow += U * rt.lanes) {
+            Vec<T, V> g[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (ow + u * rt.lanes < s.OW) g[u] = ldv<T, V>(grow + (ow + u * rt.lanes) * s.C + c);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int o = ow + u * rt.lanes;
+                if (o >= s.OW) continue;
+                float val[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) val[i] = Elem<T>::to_f(g[u].v[i]) * inv;
+                T* d = drow + o * rw * s.C + c;
+                if (accumulate) {
+                    for (int k = 0; k < rw; ++k) {
+                        float acc[V];
+#pragma unroll
+                        for (int i = 0; i < V; ++i) acc[i] = val[i];
+                        fma_vec<T, V>(acc, ldv<T, V>(d + k * s.C), 1.f);
+                        store_vec<T, V>(d + k * s.C, acc);
+                    }
+                } else {
+                    Vec<T, V> packed;
+#pragma unroll
+                    for (int i = 0; i < V; ++i) packed.v[i] = Elem<T>::from_f(val[i]);
+                    for (int k = 0; k < rw; ++k) *reinterpret_cast<Vec<T, V>*>(d + k * s.C) = packed;
+                }
+            }
+        }
+    }
+}
+
 // ---- bilinear resize (align_corners = False) ---------------------------------------------------
 struct Tap { int i0, i1; float l0, l1; };
 __device__ __forceinline__ Tap source_taps(int dst, float scale, int in) {
@@ -562,11 +649,23 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
         const T* in = static_cast<const T*>(src);
         T* out = static_cast<T*>(dst);
         [[maybe_unused]] constexpr size_t kTableMax = 40 * 1024;   // lookup tables must fit the default shared memory
+        [[maybe_unused]] const bool uniform = (H % OH == 0) && (W % OW == 0);
         if constexpr (OP == Resample::PoolFwd) {
+            const int rw = uniform ? W / OW : 0;
+            if (rw == 2 || rw == 4 || rw == 8) {
+                if (rw == 2) pool_fwd_uniform_kernel<T, V, 2><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+                else if (rw == 4) pool_fwd_uniform_kernel<T, V, 4><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+                else pool_fwd_uniform_kernel<T, V, 8><<<blocks, kRowThreads, 0, st>>>(in, out, s);
+                return check_launch();
+            }
             const size_t tab = sizeof(int) * 2 * (size_t)OW;
             if (tab <= kTableMax) pool_fwd_kernel<T, V, true><<<blocks, kRowThreads, tab, st>>>(in, out, s);
             else pool_fwd_kernel<T, V, false><<<blocks, kRowThreads, 0, st>>>(in, out, s);
         } else if constexpr (OP == Resample::PoolBwd) {
+            if (uniform) {
+                pool_bwd_uniform_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
+                return check_launch();
+            }
             const size_t tab = sizeof(int) * (2 * (size_t)W + (size_t)OW + kMaxPoolRows);
             if (tab <= kTableMax && (OH + H - 1) / H + 1 <= kMaxPoolRows) pool_bwd_seg_kernel<T, V><<<blocks, kRowThreads, tab, st>>>(in, out, s, accumulate);
             else pool_bwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, accumulate);
