@@ -484,6 +484,85 @@ __global__ void __launch_bounds__(kRowThreads) upsample_bwd_kernel(const T* __re
     }
 }
 
+// The adjoint as an in-thread scatter: a thread keeps one channel vector and a run of source columns
+// [ia, ib), and walks the destination columns that touch them in order.  For each destination column
+// the gradient is first combined over the destination rows that read this block's source row (weights
+// wy, shared by the whole block), then added to the (at most two) source columns it reads with the
+// forward weights; a source column is stored as soon as the walk has passed its last reader.  Every
+// gradient vector is fetched once per run instead of once per source column that reads it, and there
+// are no atomics: contributions to columns outside the run are simply left to the neighbouring thread.
+template <typename T, int V>
+__global__ void __launch_bounds__(kRowThreads) upsample_bwd_walk_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s,
+                                                                        float scale_h, float scale_w) {
+    extern __shared__ float tab[];
+    float* wy = tab;                                       // [kMaxTaps]
+    int* meta = reinterpret_cast<int*>(tab + kMaxTaps);    // oy0, ny
+    Tap* xt = reinterpret_cast<Tap*>(tab + kMaxTaps + 4);  // [OW] forward taps of every destination column
+    const int iy = blockIdx.x % s.H, b = blockIdx.x / s.H;
+    if (threadIdx.x == 0) {
+        int lo, hi;
+        dst_range(iy, scale_h, s.OH, &lo, &hi);
+        while (lo <= hi && tap_weight(lo, iy, scale_h, s.H) == 0.f) ++lo;
+        while (hi >= lo && tap_weight(hi, iy, scale_h, s.H) == 0.f) --hi;
+        meta[0] = lo;
+        meta[1] = hi - lo + 1;
+        for (int j = 0; j <= hi - lo && j < kMaxTaps; ++j) wy[j] = tap_weight(lo + j, iy, scale_h, s.H);
+    }
+    for (int ox = threadIdx.x; ox < s.OW; ox += kRowThreads) xt[ox] = source_taps(ox, scale_w, s.W);
+    __syncthreads();
+    const int oy0 = meta[0], ny = meta[1];
+    const int cv = s.C / V;
+    const RowThread rt = row_thread(cv);
+    if (rt.lane >= rt.lanes) return;
+    const int seg = (s.W + rt.lanes - 1) / rt.lanes;
+    const int ia = rt.lane * seg, ib = min(s.W, ia + seg);
+    if (ia >= ib) return;
+    // destination columns that read a column of [ia, ib): taps are non-decreasing in ox
+    int lo = 0, hi = s.OW;
+    while (lo < hi) { const int m = (lo + hi) >> 1; if (xt[m].i1 >= ia) hi = m; else lo = m + 1; }
+    const int ox_begin = lo;
+    lo = ox_begin; hi = s.OW;
+    while (lo < hi) { const int m = (lo + hi) >> 1; if (xt[m].i0 > ib - 1) hi = m; else lo = m + 1; }
+    const int ox_end = lo;
+    const T* gbase = go + ((size_t)b * s.OH + oy0) * s.OW * s.ld;
+    const int row_stride = s.OW * s.ld;
+    T* drow = dx + ((size_t)b * s.H + iy) * s.W * s.C;
+    for (int vec = rt.vec0; vec < cv; vec += rt.cvb) {
+        const int c = vec * V;
+        int cur = ia;                 // source column accumulated in a0; a1 belongs to cur + 1
+        float a0[V], a1[V];
+#pragma unroll
+        for (int q = 0; q < V; ++q) { a0[q] = 0.f; a1[q] = 0.f; }
+        for (int ox = ox_begin; ox < ox_end; ++ox) {
+            const Tap t = xt[ox];
+            while (cur < t.i0) {      // nobody further right reads `cur`: done
+                store_vec<T, V>(drow + cur * s.C + c, a0);
+#pragma unroll
+                for (int q = 0; q < V; ++q) { a0[q] = a1[q]; a1[q] = 0.f; }
+                ++cur;
+            }
+            float g[V];
+#pragma unroll
+            for (int q = 0; q < V; ++q) g[q] = 0.f;
+            const T* p = gbase + ox * s.ld + c;
+            for (int jy = 0; jy < ny; ++jy) fma_vec<T, V>(g, ldv<T, V>(p + jy * row_stride), wy[jy]);
+            const float w00 = (t.i0 == cur ? t.l0 : 0.f) + (t.i1 == cur ? t.l1 : 0.f);
+            const float w01 = t.i1 == cur + 1 ? t.l1 : 0.f;
+#pragma unroll
+            for (int q = 0; q < V; ++q) {
+                a0[q] = fmaf(w00, g[q], a0[q]);
+                a1[q] = fmaf(w01, g[q], a1[q]);
+            }
+        }
+        while (cur < ib) {
+            store_vec<T, V>(drow + cur * s.C + c, a0);
+#pragma unroll
+            for (int q = 0; q < V; ++q) { a0[q] = a1[q]; a1[q] = 0.f; }
+            ++cur;
+        }
+    }
+}
+
 // Same adjoint without tables, for extents the tables do not cover (very large ratios or widths).
 template <typename T, int V>
 __global__ void upsample_bwd_direct_kernel(const T* __restrict__ go, T* __restrict__ dx, const Shape s, float scale_h,
@@ -675,7 +754,13 @@ static int run_resample(const void* src, void* dst, int B, int H, int W, int C, 
             else upsample_fwd_kernel<T, V><<<blocks, kRowThreads, 0, st>>>(in, out, s, sh, sw);
         } else {
             const size_t table = sizeof(float) * (kMaxTaps + 2 + 2 * (size_t)W + (size_t)W * kMaxTaps);
-            if (max_taps_per_source(H, OH) <= kMaxTaps && max_taps_per_source(W, OW) <= kMaxTaps && table <= 40 * 1024) {
+            const size_t walk_table = sizeof(float) * (kMaxTaps + 4) + sizeof(Tap) * (size_t)OW;
+            // The walk pays when a thread's run of source columns is long enough to amortise the
+            // destination columns it shares with its neighbours' runs (measured: from four columns on).
+            const int cvec = C / V, lanes = kRowThreads / (cvec < kRowThreads ? cvec : kRowThreads);
+            if (max_taps_per_source(H, OH) <= kMaxTaps && walk_table <= 40 * 1024 && (W + lanes - 1) / lanes >= 4) {
+                upsample_bwd_walk_kernel<T, V><<<blocks, kRowThreads, walk_table, st>>>(in, out, s, sh, sw);
+            } else if (max_taps_per_source(H, OH) <= kMaxTaps && max_taps_per_source(W, OW) <= kMaxTaps && table <= 40 * 1024) {
                 upsample_bwd_kernel<T, V><<<blocks, kRowThreads, table, st>>>(in, out, s, sh, sw);
             } else {
                 const long long total = (long long)B * H * W * (C / V);

@@ -296,3 +296,15 @@ def test_very_wide_rows_take_the_table_free_kernels():
     assert_close_fp32(ops.upsample_forward(xs.cuda(), (4, 6000)).cpu().numpy(), oracle.c_upsample_fwd(xs.numpy(), (4, 6000)))
     assert_close_fp32(ops.upsample_backward(gbig.cuda(), (2, 3000)).cpu().numpy(),
                       oracle.c_upsample_bwd(gbig.numpy(), (2, 3000)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [((7, 24), (15, 50)), ((9, 24), (36, 96)), ((12, 40), (5, 17)), ((3, 33), (3, 33))])
+def test_upsample_backward_walk_variant(sizes, dtype):
+    """With many channels a thread owns a run of several source columns and the upsample adjoint runs
+    as the in-thread scatter walk; ratios up, down, fractional and identity."""
+    (h, w), (H, W) = sizes
+    C = 512 if dtype != torch.float32 else 256      # 64 channel vectors per pixel -> 4 column lanes
+    (go,) = draw([(2, H, W, C)], 1400 + h)
+    dx = ops.upsample_backward(to_dev(go, dtype), (h, w))
+    close(dtype)(dx.float().cpu().numpy(), oracle.c_upsample_bwd(rounded(go, dtype).numpy(), (h, w)), "dx")
