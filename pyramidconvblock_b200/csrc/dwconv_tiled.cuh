@@ -424,10 +424,10 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // One tile row r against filter row kh: a[kw] += sum_w g[r, w] * x[r + kh, w + kw], in chunks of
     // 16 columns; chunks that lie wholly right of the image (ragged last tile) are skipped.
     auto row_times_filter_row = [&](float2* a, const unsigned char* xs, const unsigned char* gs, int r, int kh,
-                                    int n_chunks, bool add_bias) {
-        const unsigned char* gp = gs + (size_t)r * grow_bytes + cp * (int)sizeof(pair_t);
-        const unsigned char* xp = xs + (size_t)(r + kh) * xrow_bytes + cp * (int)sizeof(pair_t);
-        for (int ch = 0; ch < n_chunks; ++ch) {
+                                    int ch_begin, int ch_end, bool add_bias) {
+        const unsigned char* gp = gs + (size_t)r * grow_bytes + (cp * (int)sizeof(pair_t) + ch_begin * kStrip * PIXB);
+        const unsigned char* xp = xs + (size_t)(r + kh) * xrow_bytes + (cp * (int)sizeof(pair_t) + ch_begin * kStrip * PIXB);
+        for (int ch = ch_begin; ch < ch_end; ++ch) {
             greg_t g[kStrip];
 #pragma unroll
             for (int o = 0; o < kStrip; ++o) {
@@ -478,14 +478,16 @@ dwconv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const int tw = tile % p.tiles_w, th = (tile / p.tiles_w) % p.tiles_h;
         const int rows_valid = min(p.TH, p.OH - th * p.TH);
         const int n_chunks = min(p.TWc, p.OW - tw * p.TWc + kStrip - 1) / kStrip;
-        for (int r = rl; r < rows_valid; r += RL) row_times_filter_row(acc, xs, gs, r, warp, n_chunks, bias_warp);
+        for (int r = rl; r < rows_valid; r += RL) row_times_filter_row(acc, xs, gs, r, warp, 0, n_chunks, bias_warp);
         if constexpr (SHARE) {
-            // Row groups of RL rows of the shared filter row, dealt round-robin; the starting warp
-            // rotates with the tile so that leftovers do not always land on the same warps.
+            // The shared filter row is cut into units of RL rows x one 16-column chunk, dealt round-robin;
+            // the starting warp rotates with the tile so that leftovers do not always land on the same warps.
             const int groups = (rows_valid + RL - 1) / RL;
-            for (int grp = (warp + NW - (it % NW)) % NW; grp < groups; grp += NW) {
+            const int units = groups * n_chunks;
+            for (int u = (warp + NW - (it % NW)) % NW; u < units; u += NW) {
+                const int grp = u / n_chunks, ch = u - grp * n_chunks;
                 const int r = grp * RL + rl;
-                if (r < rows_valid) row_times_filter_row(acc_last, xs, gs, r, K - 1, n_chunks, false);
+                if (r < rows_valid) row_times_filter_row(acc_last, xs, gs, r, K - 1, ch, ch + 1, false);
             }
         }
         __syncthreads();   // every warp is done with this stage: refill it
