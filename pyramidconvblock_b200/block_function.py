@@ -89,8 +89,10 @@ class ConvBlockFunction(torch.autograd.Function):
         per_branch = {}
         reduced = [i for i, s in enumerate(scales) if s != 1.]
         full = [i for i, s in enumerate(scales) if s == 1.]
-        fork = _Fork(x.device, overlap_branches and bool(reduced) and bool(full), [t, cat])
+        fork = _Fork(x.device, overlap_branches and bool(reduced) and bool(full), [t, cat, x])
         with fork:
+            mean = x.mean(dim=(1, 2))                                    # [B, dim]: the globally pooled branch
+            pooled = F.linear(mean, w_pool, b_pool)
             for i in reduced:
                 w = dw_weights[i]
                 k = w.shape[0]
@@ -104,11 +106,10 @@ class ConvBlockFunction(torch.autograd.Function):
             c = ops.dwconv_forward(t, w, None, 1, k // 2, 1)
             ops.gate_forward_into(c, cat[..., i * half:(i + 1) * half], inv_scale)
             per_branch[i] = [c]
-        fork.join([v for i in reduced for v in per_branch[i]])
+        fork.join([v for i in reduced for v in per_branch[i]] + [mean, pooled])
         saved = [v for i in range(len(scales)) for v in per_branch[i]]
         y = F.linear(cat, w_out, b_out)                                  # conv_out
-        mean = x.mean(dim=(1, 2))                                        # [B, dim]
-        ops.add_pooled_(y, F.linear(mean, w_pool, b_pool))               # + conv_pool(mean), broadcast
+        ops.add_pooled_(y, pooled)                                       # + conv_pool(mean), broadcast
         ctx.scales = tuple(scales)
         ctx.has_bias = (b_up is not None, b_out is not None, b_pool is not None)
         ctx.inv_scale = inv_scale
@@ -129,14 +130,7 @@ class ConvBlockFunction(torch.autograd.Function):
         g = g.contiguous()
         g2 = g.view(N, dim)
 
-        # conv_out / conv_pool: the pooled row's gradient (sum of g over the image) serves both biases
-        dpooled32 = g.sum(dim=(1, 2), dtype=torch.float32)               # [B, dim]
-        dpooled = dpooled32.to(dtype)
-        dbias = dpooled32.sum(0).to(dtype)
-        d_w_out = g2.t().mm(cat.view(N, -1))
-        dcat = g2.mm(w_out).view(B, H, W, -1)
-        d_w_pool = dpooled.t().mm(mean)
-        dmean = dpooled.mm(w_pool)                                       # [B, dim]
+        dcat = g2.mm(w_out).view(B, H, W, -1)                            # needed first: feeds the branches
 
         d_dw = [None] * n
         pos = {}
@@ -166,15 +160,24 @@ class ConvBlockFunction(torch.autograd.Function):
 
         # reduced-resolution branches on the side stream, full-resolution ones on this stream
         dpins = {}
-        fork = _Fork(x.device, overlap_branches and bool(reduced) and bool(full), [dcat] + saved)
+        fork = _Fork(x.device, overlap_branches and bool(reduced) and bool(full), [dcat, g, cat, mean] + saved)
         with fork:
+            # conv_out / conv_pool parameter gradients: nothing downstream in this function waits for
+            # them, so they ride on the side stream too.  The pooled row's gradient (sum of g over the
+            # image) serves both output biases.
+            dpooled32 = g.sum(dim=(1, 2), dtype=torch.float32)           # [B, dim]
+            dpooled = dpooled32.to(dtype)
+            dbias = dpooled32.sum(0).to(dtype)
+            d_w_out = g2.t().mm(cat.view(N, -1))
+            d_w_pool = dpooled.t().mm(mean)
+            dmean = dpooled.mm(w_pool)                                   # [B, dim]
             for i in reduced:
                 dpins[i] = branch_backward(i)
         dt = None
         for i in full:
             dpin = branch_backward(i)
             dt = dpin if dt is None else dt.add_(dpin)
-        fork.join([dpins[i] for i in reduced] + [d_dw[i] for i in reduced])
+        fork.join([dpins[i] for i in reduced] + [d_dw[i] for i in reduced] + [dbias, d_w_out, d_w_pool, dmean])
         for i in reduced:
             if dt is None:
                 dt = ops.pool_backward(dpins[i], (H, W))
