@@ -165,7 +165,8 @@ class GraphedTrainStep:
         device = x.device
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
+        with torch.cuda.stream(side), warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)   # same notice as below, for the warm-up stream
             for _ in range(warmup):
                 train_step(model, bucket, x, grad_out)
         torch.cuda.current_stream(device).wait_stream(side)
