@@ -20,9 +20,9 @@ from . import ops
 
 
 # Optional callback, set by the data-parallel helper: called from inside backward with
-# [(parameter, gradient), ...] as soon as every parameter gradient except conv_up's is final, i.e.
-# before the last two GEMMs of the backward pass, so that their reduction across ranks can overlap
-# with those GEMMs.
+# ([(parameter, gradient), ...], gradient shared by the unlisted 1-D parameters) as soon as gradients
+# are final - once for everything except conv_up (before the last two GEMMs of the backward pass) and
+# once for conv_up (before the dX GEMM) - so that their reduction across ranks overlaps those GEMMs.
 early_gradient_hook = None
 
 # The reduced-resolution branches run on a second CUDA stream beside the full-resolution ones: their
@@ -191,6 +191,8 @@ class ConvBlockFunction(torch.autograd.Function):
         dt2 = dt.view(N, -1)
         d_w_up = dt2.t().mm(x.view(N, dim))
         d_b_up = dt2.sum(0, dtype=torch.float32).to(dtype) if ctx.has_bias[0] else None
+        if early_gradient_hook is not None:        # the last parameter gradients: reduced under the dX GEMM
+            early_gradient_hook([(w_up, d_w_up)], d_b_up)
         dx = None
         if ctx.needs_input_grad[0]:
             dx = dt2.mm(w_up).view(B, H, W, dim)

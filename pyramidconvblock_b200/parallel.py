@@ -34,8 +34,8 @@ class GradientBucket:
             self.views.append(self.flat[off:off + n].view(p.shape))
             self.offsets.append(off)
             off += n
-        self._early_work = None
-        self._early_start = None
+        self._early_works = []     # all-reduces started during backward (reduce_early)
+        self._frontier = None      # index of the first parameter whose gradient they cover
 
     def pack(self):
         """Copy (and up-cast) the current ``.grad`` of every parameter into the flat buffer."""
@@ -65,56 +65,61 @@ class GradientBucket:
     def allreduce(self):
         """pack -> all_reduce(SUM) -> unpack.  A no-op reduction when there is one rank.
 
-        If ``reduce_early`` already sent a tail of the bucket during backward, only the head that
-        was not ready then is reduced now."""
-        work, start = self._early_work, self._early_start
-        self._early_work, self._early_start = None, None
-        if work is None:
+        Whatever ``reduce_early`` already sent during backward is only waited for; the head of the
+        bucket that was not ready then (if any) is reduced now."""
+        works, frontier = self._early_works, self._frontier
+        self._early_works, self._frontier = [], None
+        if frontier is None:
             self.pack()
             if self._distributed():
                 dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
         else:
-            head = [(v, p.grad) for p, v, o in zip(self.params, self.views, self.offsets) if o < start]
+            head = [(v, p.grad) for p, v in zip(self.params[:frontier], self.views[:frontier])]
             for v, g in head:
                 if g is None:
                     v.zero_()
             head = [(v, g) for v, g in head if g is not None]
             if head:
                 torch._foreach_copy_([v for v, _ in head], [g for _, g in head])
-            if start > 0:
-                dist.all_reduce(self.flat[:start], op=dist.ReduceOp.SUM, group=self.group)
-            work.wait()
+            if frontier > 0:
+                dist.all_reduce(self.flat[:self.offsets[frontier]], op=dist.ReduceOp.SUM, group=self.group)
+            for w in works:
+                w.wait()
         self.unpack()
         return self.flat
 
     def reduce_early(self, grads, shared_bias_grad=None):
-        """Called from inside backward with [(parameter, gradient), ...] that are already final.  If
-        they cover a whole tail of the bucket, that tail is packed and its all-reduce started at once
-        (asynchronously, on the communication stream) while backward goes on; ``allreduce()`` later
-        handles the rest.  Anything else is left for ``allreduce()``.  ``shared_bias_grad`` stands for
-        every 1-D parameter of the tail that is not listed (the two output biases share one gradient)."""
-        if not self._distributed() or self._early_work is not None:
+        """Called from inside backward with [(parameter, gradient), ...] that are already final.  If,
+        together with what earlier calls of this step sent, they cover a whole tail of the bucket,
+        the new part is packed and its all-reduce started at once (asynchronously, on the
+        communication stream) while backward goes on; ``allreduce()`` later handles what is left.
+        Anything else is ignored and left for ``allreduce()``.  ``shared_bias_grad`` stands for every
+        1-D parameter of the new part that is not listed (the two output biases share one gradient)."""
+        if not self._distributed():
             return
+        end = len(self.params) if self._frontier is None else self._frontier
         by_ptr = {p.data_ptr(): i for i, p in enumerate(self.params)}
         got = {}
         for p, g in grads:
             i = by_ptr.get(p.data_ptr())
-            if i is not None and g is not None:
+            if i is not None and i < end and g is not None:
                 got[i] = g
         if not got:
             return
         first = min(got)
-        for i in range(first, len(self.params)):
+        for i in range(first, end):
             if i not in got:
                 if shared_bias_grad is not None and self.params[i].dim() == 1:
                     got[i] = shared_bias_grad
                 else:
-                    return   # not a complete tail
-        idx = list(range(first, len(self.params)))
+                    return   # does not extend the reduced tail without a gap
+        idx = list(range(first, end))
         torch._foreach_copy_([self.views[i] for i in idx], [got[i] for i in idx])
-        self._early_start = self.offsets[first]
-        self._early_work = dist.all_reduce(self.flat[self._early_start:], op=dist.ReduceOp.SUM, group=self.group,
-                                           async_op=True)
+        lo = self.offsets[first]
+        hi = self.numel if end == len(self.params) else self.offsets[end]
+        self._early_works.append(dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                                 async_op=True))
+        self._frontier = first
 
 
 def shard_batch(global_batch, rank, world_size):

@@ -70,12 +70,14 @@ def _worker(rank, world, port, ret):
         bucket2 = GradientBucket(model2.parameters())
         params2 = list(model2.parameters())
         bucket2.reduce_early([(p, p.grad) for p in params2[1:] if p.dim() > 1], shared_bias_grad=params2[-1].grad)
-        started = bucket2._early_work is not None
+        started = bucket2._frontier == 1
+        bucket2.reduce_early([(params2[0], params2[0].grad)])          # second call: the remaining head
+        started = started and bucket2._frontier == 0 and len(bucket2._early_works) == 2
         bucket2.allreduce()
         ok = ok and started and all(torch.allclose(p.grad, r, rtol=1e-4, atol=1e-4) for p, r in zip(params2, reduced))
         # an incomplete tail must be left to allreduce()
         bucket2.reduce_early([(params2[2], params2[2].grad)])
-        ok = ok and bucket2._early_work is None
+        ok = ok and bucket2._frontier is None and not bucket2._early_works
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
