@@ -158,6 +158,10 @@ class GraphedTrainStep:
     After a call, ``y``, ``x.grad`` and every parameter's ``.grad`` (already reduced over the ranks)
     hold the step's results, in the same memory every time.
 
+    Outputs of earlier eager steps of the same model must not be alive when this object is built:
+    they keep the parameters' gradient accumulators bound to the stream those steps ran on (usually
+    the default stream), which a capture on another stream may not touch.
+
     If capture is not possible (for instance a collective that cannot be captured), the object falls
     back to calling ``train_step`` eagerly; ``graphed`` tells which.
     """
