@@ -55,12 +55,14 @@ def load_peaks():
     """Roofline denominators: measured HBM copy bandwidth and the FP32 FMA peak at the measured
     maximum SM clock (148 SMs x 128 lanes x 2 flop); fallback figures if the file is absent."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    peaks = {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+    peaks = {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "bf16_tflops": 1400.0, "source": "fallback"}
     if os.path.exists(path):
         with open(path) as f:
             m = json.load(f)
         peaks = {"hbm_gbs": float(m["hbm_gbs"]), "sm_max_mhz": float(m.get("sm_max_mhz", 1965.0)),
                  "source": "measured"}
+        if "bf16_tflops_sustained" in m:
+            peaks["bf16_tflops"] = float(m["bf16_tflops_sustained"])   # GEMMs timed inside a long step
     peaks["fp32_tflops"] = 148 * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
     return peaks
 
@@ -240,13 +242,27 @@ def extra_sweeps(device):
         m = ConvBlock(256, kernel_size=k).to(torch.float16).to(device)
         xg = x.clone().requires_grad_(True)
 
+        # The block is ~60 launches of 5-300 us: enqueueing them eagerly can take the host longer than
+        # the GPU needs to run them.  So two figures: the step replayed from a CUDA graph (device time)
+        # and the eager module call (what a plain training loop sees on this host).
+        try:
+            from pyramidconvblock_b200.parallel import GradientBucket, GraphedTrainStep
+            graphed_step = GraphedTrainStep(m, GradientBucket(m.parameters()), xg, go)
+            if graphed_step.graphed:
+                rec["convblock256_fwd_bwd_graphed_ms"] = round(timed(graphed_step, n=10, warm=2), 4)
+            else:
+                rec["convblock256_graph_note"] = "capture failed: %s" % getattr(graphed_step, "error", "?")
+            del graphed_step
+        except Exception as e:
+            rec["convblock256_graph_note"] = str(e).splitlines()[0][:160] if str(e) else type(e).__name__
+
         def block_step():
             xg.grad = None
             for p in m.parameters():
                 p.grad = None
             m(xg).backward(go)
 
-        rec["convblock256_fwd_bwd_ms"] = round(timed(block_step, n=5, warm=2), 4)
+        rec["convblock256_fwd_bwd_ms"] = round(timed(block_step, n=10, warm=3), 4)
         out["k%d" % k] = rec
     del x, go
     out["chain256_k13_fp16"] = literal_chain_timing(device, timed, peaks)
@@ -549,6 +565,7 @@ def main():
     half = DIM // 2
     es = 2
     kernels = {}
+    own_hbm_bytes_per_step = 0.0      # algorithmic bytes of this library's memory-bound kernels
     for (label, shape), rec in sorted(summary.items()):
         avg_ms = rec["ms"] / rec["calls"]
         entry = {"calls": rec["calls"], "kernels": rec["kernels"], "avg_ms": round(avg_ms, 4)}
@@ -573,6 +590,8 @@ def main():
             byts = pixels * c * es * (1.5 if label == "gate_fwd" else 2.5)
             entry["gbs"] = round(byts / (avg_ms * 1e-3) / 1e9, 1)
             entry["frac_hbm_peak"] = round(entry["gbs"] / peaks["hbm_gbs"], 4)
+        if "gbs" in entry:
+            own_hbm_bytes_per_step += byts * rec["calls"] / args.steps
         kernels["%s%s" % (label, list(shape))] = entry
 
     # dominant kernel: the tiled convolution on the full-resolution gate (forward + input gradient)
@@ -604,6 +623,16 @@ def main():
     for (b, h, w) in ((local_b, HEIGHT, WIDTH), (local_b, HEIGHT // 2, WIDTH // 2)):
         total_conv_flops += 3 * 2 * conv_fmas(b, h, w, half, KSIZE)
     step_roofline_ms = total_conv_flops / (peaks["fp32_tflops"] * 1e12) * 1e3
+    # Every kernel of the step at its own bound: the convolutions at the FP32 peak; the six dense GEMMs
+    # (conv_up / conv_out forward, and their two gradients each, all [pixels,512] x [512,256]-shaped) at
+    # the slower of the tensor-core peak and their operand traffic; the two full-size reductions (spatial
+    # mean of x, pooled-row gradient) and this library's gate / resample kernels at the HBM peak.
+    n_pix = local_b * HEIGHT * WIDTH
+    gemm_ms = 6 * max(2.0 * n_pix * DIM * half / (peaks["bf16_tflops"] * 1e12),
+                      n_pix * (DIM + half) * es / (peaks["hbm_gbs"] * 1e9)) * 1e3
+    reduce_ms = 2 * n_pix * DIM * es / (peaks["hbm_gbs"] * 1e9) * 1e3
+    own_hbm_ms = own_hbm_bytes_per_step / (peaks["hbm_gbs"] * 1e9) * 1e3
+    composite_ms = step_roofline_ms + gemm_ms + reduce_ms + own_hbm_ms
 
     result = {
         "metric": "convblock_train_images_per_s", "value": round(value, 2), "unit": "images/s",
@@ -618,6 +647,11 @@ def main():
         "clocks": clocks,
         "roofline": roofline,
         "step_fraction_of_conv_roofline": round(step_roofline_ms / ms_per_step, 4),
+        "step_roofline": {"conv_fp32_ms": round(step_roofline_ms, 4), "gemm_ms": round(gemm_ms, 4),
+                          "reductions_hbm_ms": round(reduce_ms, 4), "gate_resample_hbm_ms": round(own_hbm_ms, 4),
+                          "sum_ms": round(composite_ms, 4), "frac": round(composite_ms / ms_per_step, 4),
+                          "note": "each kernel of the step at its own bound (FP32 FMA peak, tensor/HBM for the "
+                                  "GEMMs, HBM for the rest), summed with no overlap assumed"},
         "kernels": kernels,
     }
     if world == 1 and not args.no_cpu_baseline:
