@@ -186,3 +186,27 @@ def ref_block_forward_backward(x, gout, params, dtype=torch.float64, scales=(1.,
     y = ref_block_forward(x, ps, scales)
     y.backward(gout.to(dtype))
     return y.detach(), x.grad, {k: v.grad for k, v in ps.items()}
+
+
+def ref_block_forward_nchw(x, params, scales=(1., 1 / 2)):
+    """The NCHW torch form of the block (ConvBlockT.forward with SimpleGateT,
+    pyramid_dwconv/conv_block.py:50-97) from a state_dict-like mapping whose weights have the
+    nn.Conv2d shapes: [O,I,1,1] for the three pointwise layers, [C,1,K,K] for the depthwise ones."""
+    t = F.conv2d(x, params["conv_up.weight"], params.get("conv_up.bias"))
+    H, W = x.shape[2], x.shape[3]
+    outs = []
+    for i, s in enumerate(scales):
+        w = params["gates.%d.conv_spatial.weight" % i]
+        C, k = w.shape[0], w.shape[-1]
+        b = t
+        if s != 1.:
+            b = F.adaptive_avg_pool2d(b, (int(H * s), int(W * s)))
+        b = F.conv2d(b, w, params.get("gates.%d.conv_spatial.bias" % i), padding=k // 2, groups=C)
+        b1, b2 = b.chunk(2, dim=1)
+        b = b1 * (b2 / (C / 2) ** -0.5)
+        if s != 1.:
+            b = F.interpolate(b, size=(H, W), mode="bilinear", align_corners=False)
+        outs.append(b)
+    t = F.conv2d(torch.cat(outs, dim=1), params["conv_out.weight"], params.get("conv_out.bias"))
+    pooled = F.conv2d(F.adaptive_avg_pool2d(x, 1), params["conv_pool.weight"], params.get("conv_pool.bias"))
+    return t + pooled
