@@ -1,6 +1,7 @@
 // Entry points of the depthwise convolution (forward, input gradient, weight/bias gradient),
 // the untiled kernels that cover every stride / dilation / padding / channel count, and the
 // library-wide helpers (tensor-map encoding, tuning knobs, status strings).
+#include <atomic>
 #include <mutex>
 
 #include "dwconv_tiled.cuh"
@@ -12,19 +13,19 @@ thread_local int g_last_cuda_error = 0;
 // ---------------------------------------------------------------------------------------------
 // Library-wide helpers
 // ---------------------------------------------------------------------------------------------
-static int g_tuning[8] = {1, 16, 0, 0, 0, 0, 0, 0};
-int tuning(int key) { return g_tuning[key]; }
+static std::atomic<int> g_tuning[8] = {1, 16, 0, 0, 0, 0, 0, 0};
+int tuning(int key) { return g_tuning[key].load(std::memory_order_relaxed); }
 
 int sm_count() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];     // zero-initialised; filled on first use per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -272,9 +273,7 @@ int pdw_last_cuda_error(void) { return g_last_cuda_error; }
 int pdw_set_tuning(int key, int value) {
     if (key < 0 || key > 7) return -1;
     if (key == 1 && value != 16 && value != 32) return -1;
-    const int prev = g_tuning[key];
-    g_tuning[key] = value;
-    return prev;
+    return g_tuning[key].exchange(value, std::memory_order_relaxed);
 }
 
 int pdw_conv_out_size(int in, int kernel, int stride, int pad, int dil) {

@@ -133,6 +133,15 @@ def _check_nhwc(x, name):
         raise RuntimeError("%s must be a 4-D [B,H,W,C] tensor, got %d-D" % (name, x.dim()))
 
 
+def _same_dtype_and_device(what, *tensors):
+    """The kernels read every operand with one element type; a mismatch would be read as garbage."""
+    first = tensors[0]
+    for t in tensors[1:]:
+        if t.dtype != first.dtype or t.device != first.device:
+            raise RuntimeError("%s: operands must share one dtype and device (got %s on %s and %s on %s)"
+                               % (what, first.dtype, first.device, t.dtype, t.device))
+
+
 def dwconv_forward(x, weight, bias=None, stride=1, padding=0, dilation=1):
     """y[B,OH,OW,C] = depthwise correlation of x[B,H,W,C] with weight[KH,KW,C] (+ bias[C])."""
     _require_cuda(x, weight, bias)
@@ -165,6 +174,9 @@ def dwconv_backward_input(grad_out, weight, input_hw, stride=1, padding=0, dilat
     _require_cuda(grad_out, weight)
     _check_nhwc(grad_out, "grad_output")
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    if weight.dim() != 3 or weight.shape[2] != grad_out.shape[3]:
+        raise RuntimeError("weight must be [KH,KW,C] with C == grad_output channels")
+    _same_dtype_and_device("dwconv_backward_input", grad_out, weight)
     grad_out, weight = grad_out.contiguous(), weight.contiguous()
     B, OH, OW, C = grad_out.shape
     H, W = input_hw
@@ -191,8 +203,7 @@ def dwconv_backward_weight(x, grad_out, kernel_size, stride=1, padding=0, dilati
     _check_nhwc(grad_out, "grad_output")
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
     k = _pair(kernel_size)
-    if x.dtype != grad_out.dtype:
-        raise RuntimeError("input and grad_output must share one dtype")
+    _same_dtype_and_device("dwconv_backward_weight", x, grad_out)
     x, grad_out = x.contiguous(), grad_out.contiguous()
     B, H, W, C = x.shape
     if tuple(grad_out.shape) != (B,) + conv_out_hw(H, W, k, stride, padding, dilation) + (C,):
@@ -273,6 +284,7 @@ def _slice_ld(t, channels, what):
 def gate_forward_into(conv_out, out_slice, inv_scale):
     """gate_forward writing into ``out_slice``, a [..., C/2] channel slice of a wider NHWC buffer."""
     _require_cuda(conv_out, out_slice)
+    _same_dtype_and_device("gate_forward_into", conv_out, out_slice)
     conv_out = conv_out.contiguous()
     C = conv_out.shape[-1]
     pixels = conv_out.numel() // C
@@ -288,6 +300,7 @@ def gate_forward_into(conv_out, out_slice, inv_scale):
 def gate_backward_from(conv_out, grad_slice, inv_scale):
     """gate_backward reading ``grad_slice``, a [..., C/2] channel slice of a wider NHWC gradient."""
     _require_cuda(conv_out, grad_slice)
+    _same_dtype_and_device("gate_backward_from", conv_out, grad_slice)
     conv_out = conv_out.contiguous()
     C = conv_out.shape[-1]
     pixels = conv_out.numel() // C
@@ -305,6 +318,10 @@ def upsample_forward_into(x, out_slice):
     """Bilinear resize of x[B,h,w,C] into ``out_slice`` [B,H,W,C], a channel slice of a wider buffer."""
     _require_cuda(x, out_slice)
     _check_nhwc(x, "input")
+    _check_nhwc(out_slice, "output slice")
+    _same_dtype_and_device("upsample_forward_into", x, out_slice)
+    if out_slice.shape[0] != x.shape[0]:
+        raise RuntimeError("output slice and input must have the same batch size")
     x = x.contiguous()
     B, H, W, C = x.shape
     OH, OW = out_slice.shape[1], out_slice.shape[2]
@@ -333,10 +350,15 @@ def upsample_backward_from(grad_slice, input_hw):
 def pool_backward_accumulate(grad_out, dx):
     """dx[B,H,W,C] += adjoint of the adaptive average pool applied to grad_out[B,OH,OW,C]."""
     _require_cuda(grad_out, dx)
+    _check_nhwc(grad_out, "grad_output")
+    _check_nhwc(dx, "accumulation target")
+    _same_dtype_and_device("pool_backward_accumulate", grad_out, dx)
     grad_out = grad_out.contiguous()
     if not dx.is_contiguous():
         raise RuntimeError("accumulation target must be contiguous")
     B, OH, OW, C = grad_out.shape
+    if dx.shape[0] != B or dx.shape[3] != C:
+        raise RuntimeError("accumulation target must have grad_output's batch size and channels")
     H, W = dx.shape[1], dx.shape[2]
     with torch.cuda.device(dx.device):
         rc = _call("pool_bwd_accumulate", (B, H, W, C, OH, OW), 1, dx.device, lambda: _lib.lib().pdw_pool_bwd_accumulate(
@@ -348,10 +370,13 @@ def pool_backward_accumulate(grad_out, dx):
 def add_pooled_(y, v, alpha=1.0):
     """In place y[b, ..., :] += alpha * v[b, :] (y: [B, ..., C] contiguous, v: [B, C])."""
     _require_cuda(y, v)
+    _same_dtype_and_device("add_pooled_", y, v)
     if not y.is_contiguous():
         raise RuntimeError("y must be contiguous")
     v = v.contiguous()
     B, C = y.shape[0], y.shape[-1]
+    if tuple(v.shape) != (B, C):
+        raise RuntimeError("v must be [B, C] = [%d, %d], got %s" % (B, C, tuple(v.shape)))
     pixels = y.numel() // (B * C)
     with torch.cuda.device(y.device):
         rc = _call("add_pooled", (B, pixels, C), 1, y.device, lambda: _lib.lib().pdw_add_pooled(
@@ -378,6 +403,7 @@ def gate_forward(conv_out, inv_scale):
 
 def gate_backward(conv_out, grad_y, inv_scale):
     _require_cuda(conv_out, grad_y)
+    _same_dtype_and_device("gate_backward", conv_out, grad_y)
     conv_out, grad_y = conv_out.contiguous(), grad_y.contiguous()
     C = conv_out.shape[-1]
     pixels = conv_out.numel() // C

@@ -308,3 +308,31 @@ def test_upsample_backward_walk_variant(sizes, dtype):
     (go,) = draw([(2, H, W, C)], 1400 + h)
     dx = ops.upsample_backward(to_dev(go, dtype), (h, w))
     close(dtype)(dx.float().cpu().numpy(), oracle.c_upsample_bwd(rounded(go, dtype).numpy(), (h, w)), "dx")
+
+
+def test_mixed_dtypes_and_wrong_shapes_are_refused_before_any_launch():
+    """Every operand of a launch is read with one element type: the wrappers refuse mismatches."""
+    h = torch.zeros((1, 8, 8, 16), device="cuda", dtype=torch.float16)
+    f = torch.zeros((1, 8, 8, 16), device="cuda", dtype=torch.float32)
+    w32 = torch.zeros((3, 3, 16), device="cuda", dtype=torch.float32)
+    with pytest.raises(RuntimeError):
+        ops.dwconv_forward(h, w32, None, 1, 1, 1)
+    with pytest.raises(RuntimeError):
+        ops.dwconv_backward_input(h, w32, (8, 8), 1, 1, 1)
+    with pytest.raises(RuntimeError):
+        ops.dwconv_backward_input(h, w32.half()[..., :8], (8, 8), 1, 1, 1)
+    with pytest.raises(RuntimeError):
+        ops.dwconv_backward_weight(h, f, 3, 1, 1, 1)
+    with pytest.raises(RuntimeError):
+        ops.gate_backward(h, f[..., :8], 1.0)
+    with pytest.raises(RuntimeError):
+        ops.pool_backward_accumulate(h[:, :4, :4], f)
+    with pytest.raises(RuntimeError):
+        ops.pool_backward_accumulate(h[:, :4, :4, :8].contiguous(), h.clone())
+    with pytest.raises(RuntimeError):
+        ops.add_pooled_(h.clone(), torch.zeros((1, 16), device="cuda", dtype=torch.float32))
+    with pytest.raises(RuntimeError):
+        ops.add_pooled_(h.clone(), torch.zeros((2, 16), device="cuda", dtype=torch.float16))
+    with pytest.raises(RuntimeError):
+        ops.upsample_forward_into(h[:, :4, :4].contiguous(), f)
+    ops.check_device_status()
