@@ -253,18 +253,22 @@ inline bool plan_fwd_tile(int OH, int OW, int KH, int K, int esize, int wreg_byt
         cands[n++] = Cand{TH, TWc, rows, cols, smem, tiles_h, tiles_w, eff, (double)tiles_h * tiles_w * n_batch_ct, two};
         if (eff > best_eff) best_eff = eff;
     };
+    // Widths that are multiples of 48 (48, 96, ...) split into 16x48 tiles without a ragged column of
+    // tiles.  Such a tile is 12 items for 8 warps, which the efficiency estimate below marks down to
+    // 0.75 although the block sharing the SM fills the idle issue slots; with tuning key 8 set the shape
+    // is taken regardless of the estimate (it then only has to yield enough blocks).
+    const bool favour_16x48 = tuning(8) != 0 && OW % 48 == 0;
     if (force_th && force_tw) {
         consider(force_th, force_tw);
     } else {
-        // Widths that are multiples of 48 (48, 96, ...) split into three-strip tiles without a ragged
-        // column of tiles; measured 2-13 % faster than 32x32 there.
         if (OW % 48 == 0) consider(16, 48);
         for (const TileShape& t : kTilePreference) consider(t.th, t.tw);
     }
     if (n == 0) return false;
     int pick = -1, most = -1;
     for (int i = 0; i < n; ++i) {
-        if (cands[i].eff < 0.97 * best_eff) continue;
+        const bool favoured = favour_16x48 && cands[i].th == 16 && cands[i].tw == 48;
+        if (cands[i].eff < 0.97 * best_eff && !favoured) continue;
         if (most < 0 || cands[i].blocks > cands[most].blocks) most = i;
         const double want = (cands[i].tw == 48 ? 2.0 : 3.0) * (cands[i].two ? 2 : 1) * sms;
         if (cands[i].blocks >= want) { pick = i; break; }

@@ -31,11 +31,14 @@ def rounded(t, dtype):
 @pytest.fixture(autouse=True)
 def _reset_tuning_and_check_status():
     L = _lib.lib()
-    defaults = ((0, 1), (1, 16), (2, 0), (7, 0))
-    for key, value in defaults:
-        L.pdw_set_tuning(key, value)
+    # the library's current settings (the setter returns the previous value), restored after the test
+    saved = []
+    for key in range(9):
+        prev = L.pdw_set_tuning(key, 16 if key == 1 else 0)
+        L.pdw_set_tuning(key, prev)
+        saved.append((key, prev))
     yield
-    for key, value in defaults:
+    for key, value in saved:
         L.pdw_set_tuning(key, value)
     ops.check_device_status()
 
@@ -92,6 +95,26 @@ def test_dwconv_inner_loop_variants_agree(k, dtype, math, ct):
     L.pdw_set_tuning(0, math)
     L.pdw_set_tuning(1, ct)
     run_conv_case(1, 40, 37, 48, k, dtype, seed=200 + k)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tile", [(16, 48), (32, 32), (16, 64), (24, 32), (32, 16), (8, 32), (4, 16), (32, 48)])
+def test_dwconv_forced_tiles_agree(tile, dtype):
+    """Every thread-block tile the planner can choose (forward / input gradient: keys 3/4, weight
+    gradient: keys 5/6) gives the oracle's result, ragged last tiles included."""
+    L = _lib.lib()
+    for key, value in ((3, tile[0]), (4, tile[1]), (5, tile[0]), (6, tile[1])):
+        L.pdw_set_tuning(key, value)
+    run_conv_case(2, 50, 100, 16, 9, dtype, seed=250 + tile[0] + tile[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k", [9, 13, 17])
+def test_dwconv_16x48_tiles_on_widths_divisible_by_48(k, dtype):
+    """Tuning key 8: 16x48 tiles are taken for 48- and 96-pixel-wide images."""
+    _lib.lib().pdw_set_tuning(8, 1)
+    run_conv_case(2, 48, 48, 32, k, dtype, seed=260 + k)
+    run_conv_case(1, 37, 96, 16, k, dtype, seed=270 + k)
 
 
 @pytest.mark.parametrize("shape", [
