@@ -203,8 +203,8 @@ int pdw_add_pooled(void* y, const void* v, int batch, int64_t pixels_per_image, 
  * key 1: channels per thread block tile, 16 or 32; key 2: force the untiled kernels when 1;
  * keys 3/4 and 5/6: force the tile rows/columns of the forward and of the weight-gradient kernel,
  * 0 = chosen by the library; key 7: 1 selects the streaming (persistent, warp-specialised) form of the
- * 16-bit forward / input-gradient kernel; key 8: 1 makes the forward / input-gradient kernel take
- * 16x48 tiles on images whose width is a multiple of 48 whatever its own estimate says).
+ * 16-bit forward / input-gradient kernel; key 8: 1 leaves out the measured per-filter-width
+ * tile preferences of the planners and keeps only their generic estimate).
  * Results are identical for every setting.  Returns the previous value, or -1 for a bad key.
  */
 int pdw_set_tuning(int key, int value);

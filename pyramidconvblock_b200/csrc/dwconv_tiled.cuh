@@ -211,22 +211,34 @@ struct TileShape { int th, tw; };
 constexpr TileShape kTilePreference[] = {{32, 32}, {16, 64}, {24, 32}, {16, 48}, {16, 32}, {32, 16},
                                          {16, 16}, {8, 32},  {8, 16},  {4, 16}};
 
-// Picks the thread-block tile for the forward / input-gradient kernel: the first shape of the
-// preference list that fits two blocks per SM, wastes (almost) no warp rounds or edge items, and
-// still yields at least three blocks per SM slot (small problems want small tiles); failing the last
-// condition, the efficient shape with the most blocks.
+// Picks the thread-block tile for the forward / input-gradient kernel.
+//
+// Generic part: the first shape of the preference list that fits two blocks per SM, wastes (almost)
+// no warp rounds or edge items, and still yields at least three blocks per SM slot (small problems
+// want small tiles); failing the last condition, the efficient shape with the most blocks.
+//
+// Measured part (16-bit tensors, 16-channel tiles; B200, k = 9/13/17 on 48..128-pixel images, 16..128
+// images): a few shapes beat the generic choice by 2-12 % and are tried first.
+//  * k >= 15: 32x16 - its 59 KB of shared memory let three blocks share an SM instead of two; on
+//    images of 33..48 rows a full-height 16-column tile (all of its vertical halo is zero fill, and
+//    filter rows that only see padding are skipped); 32x48 on widths that are multiples of 48 once
+//    the grid is at least 20 waves long (least halo per output, three warp rounds per block).
+//  * k = 9..13: a 16-row tile as wide as the image for widths 48..64; for k = 9 also 32x48 as above.
+// The warp-round estimate of the generic part does not apply to these (a 12-item tile leaves half
+// of the warps idle in its second round, but the neighbouring blocks on the SM fill those issue
+// slots).  Tuning key 8 switches the measured part off.
 template <int CT>
 inline bool plan_fwd_tile(int OH, int OW, int KH, int K, int esize, int wreg_bytes, int n_batch_ct, int sms,
                           TiledParams* p, int* smem_bytes) {
     constexpr int CPL = CT / 2, RL = 32 / CPL;
     const int pixb = CT * esize;
     const int force_th = tuning(3), force_tw = tuning(4);
-    struct Cand { int th, tw, rows, cols, smem, tiles_h, tiles_w; double eff, blocks; bool two; };
-    Cand cands[16];
+    struct Cand { int th, tw, rows, cols, smem, tiles_h, tiles_w; double eff, edge, blocks; bool two; };
+    Cand cands[20];
     int n = 0;
-    double best_eff = 0.0;
+    double best_eff = 0.0, best_edge = 0.0;
     auto consider = [&](int TH, int TWc) {
-        if (TH % RL != 0 || TWc % kStrip != 0) return;
+        if (n >= 20 || TH <= 0 || TWc <= 0 || TH % RL != 0 || TWc % kStrip != 0) return;
         const int rows = TH + KH - 1;
         int cols = TWc + K - 1;
         if (RL > 1 && (cols % 2) == 0) cols++;
@@ -249,31 +261,57 @@ inline bool plan_fwd_tile(int OH, int OW, int KH, int K, int esize, int wreg_byt
             }
         }
         const bool two = smem <= kSmemPerCta2;
-        const double eff = (work / slots) * ((double)OH * OW / (work * RL * kStrip)) * (two ? 1.0 : 0.85);
-        cands[n++] = Cand{TH, TWc, rows, cols, smem, tiles_h, tiles_w, eff, (double)tiles_h * tiles_w * n_batch_ct, two};
-        if (eff > best_eff) best_eff = eff;
+        const double edge = (double)OH * OW / (work * RL * kStrip);
+        const double eff = (work / slots) * edge * (two ? 1.0 : 0.85);
+        cands[n++] = Cand{TH, TWc, rows, cols, smem, tiles_h, tiles_w, eff, edge, (double)tiles_h * tiles_w * n_batch_ct, two};
+        if (edge > best_edge) best_edge = edge;
     };
-    // Widths that are multiples of 48 (48, 96, ...) split into 16x48 tiles without a ragged column of
-    // tiles.  Such a tile is 12 items for 8 warps, which the efficiency estimate below marks down to
-    // 0.75 although the block sharing the SM fills the idle issue slots; with tuning key 8 set the shape
-    // is taken regardless of the estimate (it then only has to yield enough blocks).
-    const bool favour_16x48 = tuning(8) != 0 && OW % 48 == 0;
+    int fav[4], nfav = 0, first_generic = 0;    // cands[0 .. first_generic) are the measured favourites
+    double fav_min_blocks[4];
+    auto favour = [&](int TH, int TWc, double min_blocks) {
+        const int before = n;
+        consider(TH, TWc);
+        if (n > before && nfav < 4) { fav[nfav] = before; fav_min_blocks[nfav] = min_blocks; ++nfav; }
+    };
     if (force_th && force_tw) {
         consider(force_th, force_tw);
     } else {
-        if (OW % 48 == 0) consider(16, 48);
+        if (esize == 2 && CT == 16 && tuning(8) == 0) {
+            const double long_grid = 20.0 * 2 * sms;
+            if (K >= 15) {
+                if (OH > 32 && OH <= 48) favour(OH, 16, 0.0);
+                if (OW % 48 == 0) favour(32, 48, long_grid);
+                favour(32, 16, 0.0);
+            } else if (K >= 9) {
+                if (OW >= 48 && OW <= 64) favour(16, OW, 0.0);
+                if (K == 9 && OW % 48 == 0) favour(32, 48, long_grid);
+            }
+        }
+        first_generic = n;
         for (const TileShape& t : kTilePreference) consider(t.th, t.tw);
     }
     if (n == 0) return false;
+    best_eff = 0.0;
+    for (int i = first_generic; i < n; ++i) best_eff = cands[i].eff > best_eff ? cands[i].eff : best_eff;
     int pick = -1, most = -1;
-    for (int i = 0; i < n; ++i) {
-        const bool favoured = favour_16x48 && cands[i].th == 16 && cands[i].tw == 48;
-        if (cands[i].eff < 0.97 * best_eff && !favoured) continue;
+    // a measured favourite: enough blocks for one full wave (and for its own condition), no more edge
+    // waste than the best shape
+    for (int i = 0; i < nfav && pick < 0; ++i) {
+        const Cand& c = cands[fav[i]];
+        const double need = fav_min_blocks[i] > 2.0 * sms ? fav_min_blocks[i] : 2.0 * sms;
+        if (c.blocks >= need && c.edge >= 0.97 * best_edge) pick = fav[i];
+    }
+    for (int i = first_generic; i < n && pick < 0; ++i) {
+        if (cands[i].eff < 0.97 * best_eff) continue;
         if (most < 0 || cands[i].blocks > cands[most].blocks) most = i;
-        const double want = (cands[i].tw == 48 ? 2.0 : 3.0) * (cands[i].two ? 2 : 1) * sms;
+        const double want = 3.0 * (cands[i].two ? 2 : 1) * sms;
         if (cands[i].blocks >= want) { pick = i; break; }
     }
     if (pick < 0) pick = most;
+    if (pick < 0) {                 // no generic shape fits: fall back on a favourite if there is one
+        if (nfav == 0) return false;
+        pick = fav[0];
+    }
     const Cand& c = cands[pick];
     p->TH = c.th; p->TWc = c.tw; p->rows = c.rows; p->cols = c.cols;
     p->tiles_h = c.tiles_h; p->tiles_w = c.tiles_w;
@@ -575,7 +613,7 @@ inline bool plan_wgrad(int B, int OH, int OW, int C, int KH, int esize, int sms,
     int n = 0;
     double best_eff = 0.0;
     auto consider = [&](int TH, int TWc) {
-        if (TH % RL != 0 || TWc % kStrip != 0) return;
+        if (n >= 16 || TH % RL != 0 || TWc % kStrip != 0) return;
         const int xrows = TH + KH - 1;
         int xcols = TWc + K - 1, gcols = TWc;
         if (RL > 1 && (xcols % 2) == 0) xcols++;
@@ -597,6 +635,13 @@ inline bool plan_wgrad(int B, int OH, int OW, int C, int KH, int esize, int sms,
     if (force_th && force_tw) {
         consider(force_th, force_tw);
     } else {
+        // Measured on B200 (16-bit tensors, k = 9/13/17): a 16-row tile as wide as the image is 3-8 %
+        // faster on 48-pixel-wide images (and on 64-pixel-wide ones up to k = 13); k <= 13 also gains
+        // 1-3 % from 16x64 tiles on widths that are multiples of 64.  Tuning key 8 switches this off.
+        if (esize == 2 && CT == 16 && K >= 9 && tuning(8) == 0) {
+            if (OW == 48 || (K <= 13 && OW > 48 && OW <= 64)) consider(16, OW);
+            if (K <= 13 && OW % 64 == 0) consider(16, 64);
+        }
         for (const TileShape& t : kTilePreference) consider(t.th, t.tw);
     }
     int pick = -1;

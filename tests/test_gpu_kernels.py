@@ -108,13 +108,40 @@ def test_dwconv_forced_tiles_agree(tile, dtype):
     run_conv_case(2, 50, 100, 16, 9, dtype, seed=250 + tile[0] + tile[1])
 
 
+@pytest.mark.parametrize("generic", [0, 1])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("k", [9, 13, 17])
-def test_dwconv_16x48_tiles_on_widths_divisible_by_48(k, dtype):
-    """Tuning key 8: 16x48 tiles are taken for 48- and 96-pixel-wide images."""
-    _lib.lib().pdw_set_tuning(8, 1)
+def test_dwconv_planner_choices_on_48_to_128_pixel_images(k, dtype, generic):
+    """Image sizes for which the planners hold measured tile preferences (full-width 16-row tiles on
+    48..64-pixel widths, full-height tiles on 33..48 rows, 32x16 for wide filters), with those
+    preferences on (tuning key 8 = 0, the default) and off."""
+    _lib.lib().pdw_set_tuning(8, generic)
     run_conv_case(2, 48, 48, 32, k, dtype, seed=260 + k)
     run_conv_case(1, 37, 96, 16, k, dtype, seed=270 + k)
+    run_conv_case(1, 64, 64, 16, k, dtype, seed=280 + k)
+    run_conv_case(1, 40, 128, 16, k, dtype, seed=290 + k)
+
+
+@pytest.mark.parametrize("k", [9, 17])
+def test_dwconv_long_grid_tile_equals_generic_tile(k):
+    """On a grid of more than 20 waves a 96-pixel-wide image takes 32x48 tiles; the tile shape changes
+    neither the taps an output sums nor their order, so the result equals the 32x32-tile one bit for bit."""
+    L = _lib.lib()
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn((8, 96, 96, 2048), generator=gen, device="cuda").bfloat16()
+    w = (torch.randn((k, k, 2048), generator=gen, device="cuda") / k).bfloat16()
+    y = ops.dwconv_forward(x, w, None, 1, k // 2, 1)
+    dx = ops.dwconv_backward_input(x, w, (96, 96), 1, k // 2, 1)
+    L.pdw_set_tuning(3, 32)
+    L.pdw_set_tuning(4, 32)
+    y32 = ops.dwconv_forward(x, w, None, 1, k // 2, 1)
+    dx32 = ops.dwconv_backward_input(x, w, (96, 96), 1, k // 2, 1)
+    assert torch.equal(y, y32) and torch.equal(dx, dx32)
+    # and a spot check of the values themselves on one image and a few channels
+    xs = x[:1, :, :, :16].contiguous()
+    ws = w[:, :, :16].contiguous()
+    ref = oracle.c_dwconv_fwd(xs.float().cpu(), ws.float().cpu(), None, 1, k // 2, 1)
+    close(torch.bfloat16)(y[:1, :, :, :16].float().cpu().numpy(), ref, "y")
 
 
 @pytest.mark.parametrize("shape", [
