@@ -665,7 +665,7 @@ def main():
 
 # DRAM bytes (read + write) of one dwconv_tiled_kernel launch per image of [96,96,256] bf16, k=17,
 # from the ncu capture summarised under profiles/ (traffic grows in proportion to the images of a launch).
-TRAFFIC_BYTES_PER_IMAGE = 8.34e6   # 266.9 MB for 32 images (profiles/dwconv_tiled_fwd_k17_bf16_32x96x96x256.md)
+TRAFFIC_BYTES_PER_IMAGE = 8.32e6   # 266.2 MB for 32 images (profiles/dwconv_tiled_fwd_k17_bf16_32x96x96x256.md)
 
 if __name__ == "__main__":
     main()

@@ -2,17 +2,20 @@
 
     python -m pyramidconvblock_b200.profile_cases CASE [--k 17] [--dtype bf16] [--batch 32]
                                                    [--size 96] [--channels 256] [--iters 3]
+                                                   [--tile TH TW]
 
 CASE is one of dwconv_fwd, dwconv_bwd_input, dwconv_bwd_weight, pool_fwd, pool_bwd, upsample_fwd,
 upsample_bwd, gate_fwd, gate_bwd.  The default tensors ([32,96,96,256] 16-bit = 151 MB each) are
 larger than the 126 MB L2, so DRAM counters mean something, yet hold well under 1 GB on the
-device.  Prints the average launch time measured with CUDA events.
+device.  ``--tile`` forces the thread-block tile of the convolution kernels (the planner's choice
+depends on the batch size; this reproduces the tile of a larger batch on the small capture).
+Prints the average launch time measured with CUDA events.
 """
 import argparse
 
 import torch
 
-from . import ops
+from . import _lib, ops
 
 DTYPES = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 
@@ -27,7 +30,11 @@ def main():
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--small", type=int, default=0, help="pooled / pre-upsample extent (default size/2)")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--tile", type=int, nargs=2, metavar=("TH", "TW"), help="force the convolution tile")
     a = ap.parse_args()
+    if a.tile:
+        for key, value in ((3, a.tile[0]), (4, a.tile[1]), (5, a.tile[0]), (6, a.tile[1])):
+            _lib.lib().pdw_set_tuning(key, value)
     dt = DTYPES[a.dtype]
     dev = torch.device("cuda", 0)
     B, S, C, k = a.batch, a.size, a.channels, a.k
