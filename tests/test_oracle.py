@@ -128,3 +128,51 @@ def test_known_answers():
     const = np.full((1, 9, 7, 2), 3.25, np.float32)
     assert np.allclose(oracle.c_pool_fwd(const, (4, 3)), 3.25)
     assert np.allclose(oracle.c_upsample_fwd(const, (18, 15)), 3.25)
+
+
+# ---------------------------------------------------------------------------------------------
+# Adjoint identities: every backward restatement is the transpose of its forward (which the golden
+# vectors above pin to the reference).  <A x, g> == <x, A^T g> up to fp32 output rounding.
+# ---------------------------------------------------------------------------------------------
+def _dot(a, b):
+    return float(np.sum(a.astype(np.float64) * b.astype(np.float64)))
+
+
+@pytest.mark.parametrize("geom", [
+    dict(k=(9, 9), stride=1, padding=4, dilation=1),
+    dict(k=(17, 17), stride=1, padding=8, dilation=1),
+    dict(k=(5, 3), stride=(2, 1), padding=(0, 2), dilation=1),
+    dict(k=(3, 3), stride=2, padding=1, dilation=2),
+    dict(k=(7, 7), stride=1, padding=0, dilation=1),
+])
+def test_c_oracle_conv_backward_is_the_adjoint_of_forward(geom):
+    rng = np.random.default_rng(31)
+    k = geom["k"]
+    x = rng.standard_normal((2, 19, 23, 8)).astype(np.float32)
+    w = rng.standard_normal(k + (8,)).astype(np.float32)
+    y = oracle.c_dwconv_fwd(x, w, None, geom["stride"], geom["padding"], geom["dilation"])
+    g = rng.standard_normal(y.shape).astype(np.float32)
+    dx = oracle.c_dwconv_bwd_input(g, w, (19, 23), geom["stride"], geom["padding"], geom["dilation"])
+    dw, db = oracle.c_dwconv_bwd_weight(x, g, k, geom["stride"], geom["padding"], geom["dilation"])
+    ref = _dot(y, g)
+    scale = float(np.sqrt(_dot(y, y) * _dot(g, g)))
+    assert abs(_dot(x, dx) - ref) <= 1e-5 * scale          # linear in x
+    assert abs(_dot(w, dw) - ref) <= 1e-5 * scale          # and in w
+    np.testing.assert_allclose(db, g.astype(np.float64).sum(axis=(0, 1, 2)), rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("sizes", [((16, 16), (8, 8)), ((15, 9), (4, 7)), ((96, 96), (48, 48)), ((5, 6), (9, 8)),
+                                   ((7, 7), (1, 1))])
+def test_c_oracle_resample_backward_is_the_adjoint_of_forward(sizes):
+    (H, W), (h, w) = sizes
+    rng = np.random.default_rng(32)
+    big = rng.standard_normal((2, H, W, 4)).astype(np.float32)
+    small = rng.standard_normal((2, h, w, 4)).astype(np.float32)
+    # pool: [H,W] -> [h,w];  its adjoint maps [h,w] -> [H,W]
+    lhs = _dot(oracle.c_pool_fwd(big, (h, w)), small)
+    rhs = _dot(big, oracle.c_pool_bwd(small, (H, W)))
+    assert abs(lhs - rhs) <= 1e-5 * max(1.0, abs(lhs))
+    # upsample: [h,w] -> [H,W];  its adjoint maps [H,W] -> [h,w]
+    lhs = _dot(oracle.c_upsample_fwd(small, (H, W)), big)
+    rhs = _dot(small, oracle.c_upsample_bwd(big, (h, w)))
+    assert abs(lhs - rhs) <= 1e-5 * max(1.0, abs(lhs))
