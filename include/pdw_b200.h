@@ -204,7 +204,9 @@ int pdw_add_pooled(void* y, const void* v, int batch, int64_t pixels_per_image, 
  * keys 3/4 and 5/6: force the tile rows/columns of the forward and of the weight-gradient kernel,
  * 0 = chosen by the library; key 7: 1 selects the streaming (persistent, warp-specialised) form of the
  * 16-bit forward / input-gradient kernel; key 8: 1 leaves out the measured per-filter-width
- * tile preferences of the planners and keeps only their generic estimate).
+ * tile preferences of the planners and keeps only their generic estimate; key 9: how strips at the left /
+ * right image border leave out their zero-padding columns, 0 = chosen per filter width, 1 = inside one copy
+ * of the row loop, 2 = separate copies of the row loop).
  * Results are identical for every setting.  Returns the previous value, or -1 for a bad key.
  */
 int pdw_set_tuning(int key, int value);

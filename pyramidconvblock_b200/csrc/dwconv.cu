@@ -13,7 +13,7 @@ thread_local int g_last_cuda_error = 0;
 // ---------------------------------------------------------------------------------------------
 // Library-wide helpers
 // ---------------------------------------------------------------------------------------------
-static std::atomic<int> g_tuning[9] = {1, 16, 0, 0, 0, 0, 0, 0, 0};
+static std::atomic<int> g_tuning[10] = {1, 16, 0, 0, 0, 0, 0, 0, 0, 0};
 int tuning(int key) { return g_tuning[key].load(std::memory_order_relaxed); }
 
 int sm_count() {
@@ -271,7 +271,7 @@ const char* pdw_status_string(int status) {
 int pdw_last_cuda_error(void) { return g_last_cuda_error; }
 
 int pdw_set_tuning(int key, int value) {
-    if (key < 0 || key > 8) return -1;
+    if (key < 0 || key > 9) return -1;
     if (key == 1 && value != 16 && value != 32) return -1;
     return g_tuning[key].exchange(value, std::memory_order_relaxed);
 }

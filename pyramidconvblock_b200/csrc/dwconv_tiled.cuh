@@ -51,6 +51,7 @@ struct TiledParams {
     int rows, cols;       // shared-memory tile extents (with halo; cols odd)
     int tiles_w, tiles_h, nct;
     int n_items, n_strips;
+    int one_row_loop;     // 1: border strips skip their padding columns inside the one row loop (conv_rows_seg)
     int32_t* status;
 };
 
@@ -88,6 +89,56 @@ __device__ __forceinline__ void conv_rows(float2 (&acc)[kStrip], const unsigned 
                     if (o >= 0 && o < kStrip) ffma2(acc[o], xf, wr[kw]);
                 }
             }
+        }
+        xp += row_bytes;
+        wp += K * CPL;
+    }
+}
+
+// The same with the column range cut into three segments of one straight-line body: the K/2 input
+// columns left of the strip, the middle, and the K/2 columns right of it.  A strip at the left (right)
+// image border with "same" padding passes skip_lo (skip_hi): those columns are zero padding, so the
+// segment is jumped over (warp-uniform branch).  One copy of the row loop serves all three kinds of strip.
+template <typename T, int K, int CT, bool MIXED>
+__device__ __forceinline__ void conv_rows_seg(float2 (&acc)[kStrip], const unsigned char* xp,
+                                              const typename WReg<T, MIXED>::type* wp, int n_rows, int row_bytes,
+                                              bool skip_lo, bool skip_hi) {
+    using E = Elem<T>;
+    using pair_t = typename E::pair_t;
+    using wreg_t = typename WReg<T, MIXED>::type;
+    constexpr int CPL = CT / 2;
+    constexpr int PIXB = CT * (int)sizeof(T);
+    constexpr int J0 = K / 2, J1 = kStrip + K - 1 - K / 2, J2 = kStrip + K - 1;
+    for (int r = 0; r < n_rows; ++r) {
+        wreg_t wr[K];
+#pragma unroll
+        for (int kw = 0; kw < K; ++kw) wr[kw] = wp[kw * CPL];
+        auto column = [&](int j) {
+            const pair_t xv = *reinterpret_cast<const pair_t*>(xp + j * PIXB);
+            if constexpr (MIXED) {
+#pragma unroll
+                for (int kw = 0; kw < K; ++kw) {
+                    const int o = j - kw;
+                    if (o >= 0 && o < kStrip) fma_mixed<T>(acc[o], xv, wr[kw]);
+                }
+            } else {
+                const float2 xf = E::unpack(xv);
+#pragma unroll
+                for (int kw = 0; kw < K; ++kw) {
+                    const int o = j - kw;
+                    if (o >= 0 && o < kStrip) ffma2(acc[o], xf, wr[kw]);
+                }
+            }
+        };
+        if (!skip_lo) {
+#pragma unroll
+            for (int j = 0; j < J0; ++j) column(j);
+        }
+#pragma unroll
+        for (int j = J0; j < J1; ++j) column(j);
+        if (!skip_hi) {
+#pragma unroll
+            for (int j = J1; j < J2; ++j) column(j);
         }
         xp += row_bytes;
         wp += K * CPL;
@@ -181,12 +232,16 @@ dwconv_tiled_kernel(const __grid_constant__ CUtensorMap tmap, const TiledParams 
         // are zero padding, so those input columns are neither read nor multiplied (a separate copy
         // of the row loop with a compile-time narrower column range; warp-uniform choice).
         // Measured on B200: 2-9 % faster for K = 9 and 17, 4 % slower for K = 13 (three copies of the
-        // row loop), so the middle widths keep the single loop.
+        // row loop), so the middle widths use the one segmented loop below instead.
         constexpr bool kBorderCopies = (K <= 9) || (K >= 15);
         const int ow_first = ow_tile + ocol;
         const bool same_pad = kBorderCopies && p.pad_w == K / 2 && p.OW == p.W;
         const int edge = !same_pad ? 0 : (ow_first == 0 ? 1 : (ow_first + kStrip == p.OW ? 2 : 0));
-        if (edge == 1)
+        if (p.one_row_loop) {
+            const bool pad_cols = p.pad_w == K / 2 && p.OW == p.W;
+            conv_rows_seg<T, K, CT, MIXED>(acc, xp, wp, kh_hi - kh_lo, row_bytes, pad_cols && ow_first == 0,
+                                           pad_cols && ow_first + kStrip == p.OW);
+        } else if (edge == 1)
             conv_rows<T, K, CT, MIXED, K / 2, kStrip + K - 1>(acc, xp, wp, kh_hi - kh_lo, row_bytes);
         else if (edge == 2)
             conv_rows<T, K, CT, MIXED, 0, kStrip + K - 1 - K / 2>(acc, xp, wp, kh_hi - kh_lo, row_bytes);
@@ -330,6 +385,12 @@ int launch_tiled(const TiledArgs& a) {
     p.KH = a.KH; p.pad_h = a.pad_h; p.pad_w = a.pad_w; p.flip = a.flip;
     p.nct = ceil_div(a.C, CT);
     p.status = a.status;
+    // Border strips leave out their zero-padding columns either through separate copies of the row loop
+    // (compile-time column ranges, K <= 9 and K >= 15) or inside one row loop cut into three segments.
+    // Measured on B200 (bf16/fp16, fraction of the FP32 peak on [128,96,96,256]): k=17 copies 0.746 vs one
+    // loop 0.726; k=9 0.655 vs 0.606; k=13 (which has no copies: they cost more than they saved) plain
+    // loop 0.670 vs one segmented loop 0.689.  Tuning key 9: 0 = that choice, 1 = one loop, 2 = copies.
+    p.one_row_loop = tuning(9) == 0 ? (K >= 11 && K <= 13) : (tuning(9) == 1);
     int smem = 0;
     if (!plan_fwd_tile<CT>(a.OH, a.OW, a.KH, K, (int)sizeof(T), (int)sizeof(wreg_t), a.B * p.nct, sm_count(), &p, &smem))
         return PDW_ERR_UNSUPPORTED;

@@ -33,7 +33,7 @@ def _reset_tuning_and_check_status():
     L = _lib.lib()
     # the library's current settings (the setter returns the previous value), restored after the test
     saved = []
-    for key in range(9):
+    for key in range(10):
         prev = L.pdw_set_tuning(key, 16 if key == 1 else 0)
         L.pdw_set_tuning(key, prev)
         saved.append((key, prev))
@@ -142,6 +142,19 @@ def test_dwconv_long_grid_tile_equals_generic_tile(k):
     ws = w[:, :, :16].contiguous()
     ref = oracle.c_dwconv_fwd(xs.float().cpu(), ws.float().cpu(), None, 1, k // 2, 1)
     close(torch.bfloat16)(y[:1, :, :, :16].float().cpu().numpy(), ref, "y")
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("k", [3, 9, 13, 17])
+def test_dwconv_border_strip_variants(k, dtype, mode):
+    """Tuning key 9: border strips skip their padding columns inside one copy of the row loop (1) or in
+    separate copies of it (2); the library's own choice per filter width is what every other test runs."""
+    _lib.lib().pdw_set_tuning(9, mode)
+    run_conv_case(2, 21, 48, 16, k, dtype, seed=600 + k)    # width a multiple of 16: both border strips skip
+    run_conv_case(1, 40, 37, 24, k, dtype, seed=610 + k)    # ragged right edge
+    run_conv_case(1, 16, 16, 8, k, dtype, seed=620 + k)     # one strip that is left and right border at once
+    run_conv_case(1, 20, 32, 8, k, dtype, seed=630 + k, padding=(k // 2, 1))   # not "same" padding: no skipping
 
 
 @pytest.mark.parametrize("shape", [
