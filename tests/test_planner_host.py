@@ -1,0 +1,25 @@
+"""The tile planners of the convolution kernels are plain host code: compile them into a small host
+program (no device code is run) and check, over ~1M combinations of image size, filter width, batch,
+channels and element size, that every chosen tile satisfies what the kernels and the TMA descriptors
+need (tile multiples, box extents <= 256, shared-memory budget, stage alignment, grid coverage)."""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+from conftest import ROOT
+
+
+def test_planners_only_choose_valid_tiles(tmp_path):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    exe = str(tmp_path / "planner_check")
+    src = os.path.join(ROOT, "tests", "planner_check.cu")
+    build = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-o", exe, src],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-2000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout[-3000:]
+    assert "0 failures" in run.stdout
