@@ -102,3 +102,22 @@ def test_product_package_does_not_import_the_oracle():
     code = ("import sys; sys.path.insert(0, %r); import pyramid_dwconv, pyramidconvblock_b200; "
             "assert not any(m == 'oracle' or m.startswith('oracle.') for m in sys.modules), 'oracle imported'" % ROOT)
     subprocess.run([sys.executable, "-c", code], check=True)
+
+
+def test_channel_slice_layout_check():
+    """The *_strided entry points take a pixel stride; the wrapper derives it from the tensor and
+    refuses layouts that are not a channel slice of a dense NHWC buffer (pure stride arithmetic)."""
+    from pyramidconvblock_b200 import ops
+    wide = torch.zeros(2, 5, 7, 40)
+    assert ops._slice_ld(wide, 40, "t") == 40
+    assert ops._slice_ld(wide[..., 8:24], 16, "t") == 40
+    assert ops._slice_ld(wide[:1, :, :, 8:24], 16, "t") == 40          # a batch of one may have any stride
+    assert ops._slice_ld(torch.zeros(35, 16), 16, "t") == 16           # [pixels, C]
+    with pytest.raises(RuntimeError):
+        ops._slice_ld(wide[..., 8:24], 8, "t")                          # wrong channel count
+    with pytest.raises(RuntimeError):
+        ops._slice_ld(wide[..., ::2], 20, "t")                          # strided channels
+    with pytest.raises(RuntimeError):
+        ops._slice_ld(wide[:, :, ::2, 8:24], 16, "t")                   # every other column
+    with pytest.raises(RuntimeError):
+        ops._slice_ld(wide[..., 8:24].permute(0, 2, 1, 3), 16, "t")     # rows and columns swapped
