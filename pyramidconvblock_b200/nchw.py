@@ -14,8 +14,6 @@ layout copy:
   into those of the other (1x1 conv weight [O,I,1,1] <-> Linear weight [O,I]; depthwise weight
   [C,1,KH,KW] <-> [KH,KW,C]), so a checkpoint of an NCHW model loads into the NHWC block and back.
 """
-import torch
-
 from .modules import ConvBlock
 
 
