@@ -176,3 +176,49 @@ def test_c_oracle_resample_backward_is_the_adjoint_of_forward(sizes):
     lhs = _dot(oracle.c_upsample_fwd(small, (H, W)), big)
     rhs = _dot(small, oracle.c_upsample_bwd(big, (h, w)))
     assert abs(lhs - rhs) <= 1e-5 * max(1.0, abs(lhs))
+
+
+# ---------------------------------------------------------------------------------------------
+# Randomised geometry: the C restatement against the torch ops the reference names as its CPU
+# equivalent (F.conv2d(groups=C), adaptive_avg_pool2d, bilinear interpolate), forward and backward.
+# ---------------------------------------------------------------------------------------------
+from hypothesis import given, settings, HealthCheck  # noqa: E402
+from hypothesis import strategies as st  # noqa: E402
+
+
+@settings(max_examples=40, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+@given(st.data())
+def test_c_oracle_matches_torch_conv_random_geometry(data):
+    kh, kw = data.draw(st.integers(1, 7)), data.draw(st.integers(1, 7))
+    sh, sw = data.draw(st.integers(1, 3)), data.draw(st.integers(1, 3))
+    dh, dw_ = data.draw(st.integers(1, 2)), data.draw(st.integers(1, 2))
+    ph, pw = data.draw(st.integers(0, 4)), data.draw(st.integers(0, 4))
+    H = data.draw(st.integers(dh * (kh - 1) + 1, 14))
+    W = data.draw(st.integers(dw_ * (kw - 1) + 1, 14))
+    B, C = data.draw(st.integers(1, 2)), data.draw(st.integers(1, 5))
+    seed = data.draw(st.integers(0, 10 ** 6))
+    k, s, p, d = (kh, kw), (sh, sw), (ph, pw), (dh, dw_)
+    x, w, b = draw([(B, H, W, C), k + (C,), (C,)], seed)
+    xt, wt, bt = (t.double().requires_grad_(True) for t in (x, w, b))
+    y = oracle.torch_dwconv(xt, wt, bt, s, p, d)
+    (go,) = draw([tuple(y.shape)], seed + 1)
+    y.backward(go.double())
+    assert_close_fp32(oracle.c_dwconv_fwd(x, w, b, s, p, d), y.detach().numpy())
+    assert_close_fp32(oracle.c_dwconv_bwd_input(go, w, (H, W), s, p, d), xt.grad.numpy())
+    dw, db = oracle.c_dwconv_bwd_weight(x, go, k, s, p, d)
+    assert_close_fp32(dw, wt.grad.numpy())
+    assert_close_fp32(db, bt.grad.numpy())
+
+
+@settings(max_examples=40, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+@given(st.integers(1, 20), st.integers(1, 20), st.integers(1, 20), st.integers(1, 20), st.integers(0, 10 ** 6))
+def test_c_oracle_matches_torch_resample_random_sizes(H, W, OH, OW, seed):
+    (x,) = draw([(2, H, W, 3)], seed)
+    for torch_op, c_fwd, c_bwd in ((oracle.torch_pool, oracle.c_pool_fwd, oracle.c_pool_bwd),
+                                   (oracle.torch_upsample, oracle.c_upsample_fwd, oracle.c_upsample_bwd)):
+        xt = x.double().requires_grad_(True)
+        y = torch_op(xt, (OH, OW))
+        (go,) = draw([tuple(y.shape)], seed + 1)
+        y.backward(go.double())
+        assert_close_fp32(c_fwd(x.numpy(), (OH, OW)), y.detach().numpy())
+        assert_close_fp32(c_bwd(go.numpy(), (H, W)), xt.grad.numpy())
